@@ -1,0 +1,30 @@
+// Shared between the grouping, the FP32 grouped kernels and the tensor-core grouped GEMM: the workspace tables and
+// the tensor-core entry.
+#pragma once
+
+#include "common.cuh"
+
+namespace sb {
+
+struct RouteTables {
+    const int32_t *offsets, *slots, *tile_bucket, *tile_start, *wtile_bucket, *wtile_start;
+};
+// The tables inside a grouping workspace for S slots over E experts.
+__host__ __device__ inline RouteTables route_tables(const int32_t *ws, int64_t S, int64_t E) {
+    const int64_t Tmax = S / 16 + E + 2, WTmax = S / 64 + E + 2;
+    RouteTables t;
+    t.offsets = ws + 4;
+    t.slots = t.offsets + E + 2;
+    t.tile_bucket = t.slots + S;
+    t.tile_start = t.tile_bucket + Tmax;
+    t.wtile_bucket = t.tile_start + Tmax;
+    t.wtile_start = t.wtile_bucket + WTmax;
+    return t;
+}
+
+// Tensor-core grouped projection over a grouping workspace (grouped_umma.cu). combine = false: inputs x[slot / A],
+// outputs y[slot, :] in the activation dtype. combine = true: inputs h[slot], outputs FP32 partial[slot, :].
+int grouped_umma(const char *fn, const void *x, const StackView &w, const int32_t *ws, int64_t M, int64_t A, void *y,
+                 float *partial, int act, bool combine, cudaStream_t stream);
+
+}  // namespace sb

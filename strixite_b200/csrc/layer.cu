@@ -1,0 +1,294 @@
+// The MoE sublayer as one object: the sequence strixite's Qwen4ExpSession::forward runs per layer
+// (runtime/qwen4exp.cpp:1126-1186) over the library's own entry points, with the session buffers it needs.
+// Nothing here computes: it validates, owns workspaces, picks the per-slot or grouped experts path and enqueues.
+#include "common.cuh"
+
+#include "strixite_b200.h"
+
+#include <cstring>
+#include <new>
+
+namespace {
+
+using namespace sb;
+
+// logits[m, e] += bias[e] for e < E (a harness-side routing skew; not part of the reference's layer).
+__global__ void __launch_bounds__(256) add_bias_kernel(float *logits, int64_t ld, int64_t M, int64_t E, const float *bias) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= M * E) return;
+    const int64_t m = i / E, e = i - m * E;
+    logits[m * ld + e] += bias[e];
+}
+
+// The stacked shared slot with a constant coefficient: ids[m, k] = shared_id, coef[m, k] = 1 after the router wrote
+// the k routed slots with row stride A = k + 1.
+__global__ void __launch_bounds__(256) fill_shared_slot_kernel(int32_t *ids, float *coef, int64_t M, int64_t A, int32_t shared_id) {
+    const int64_t m = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (m >= M) return;
+    const bool failed = ids[m * A] < 0;  // a token the router failed keeps -1 / NaN in every slot
+    ids[m * A + A - 1] = failed ? -1 : shared_id;
+    coef[m * A + A - 1] = failed ? qnan() : 1.0f;
+}
+
+// The router writes rows of k entries; re-spread them to stride A = k + 1 (back to front, one block per token row would
+// race across rows, so one thread walks a token: k <= 32 entries).
+__global__ void __launch_bounds__(256) widen_rows_kernel(const int32_t *ids_in, const float *coef_in, int32_t *ids, float *coef,
+                                                         int64_t M, int64_t k) {
+    const int64_t m = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (m >= M) return;
+    for (int64_t a = 0; a < k; ++a) ids[m * (k + 1) + a] = ids_in[m * k + a], coef[m * (k + 1) + a] = coef_in[m * k + a];
+}
+
+template <typename T>
+int dev_alloc(T **p, size_t n, const char *what) {
+    SB_CUDA(cudaMalloc(reinterpret_cast<void **>(p), n * sizeof(T) > 0 ? n * sizeof(T) : 16), "allocating ", what, " (", n * sizeof(T), " B)");
+    return 0;
+}
+
+}  // namespace
+
+struct strix_moe_layer {
+    strix_moe_layer_desc d;
+    int64_t A, Estack, router_rows;
+    bool gated;
+    // session buffers (strixite runtime/qwen4exp.cpp:297-380)
+    float *logits = nullptr;       // [max_tokens, router_rows]
+    int32_t *ids = nullptr, *ids_k = nullptr;  // [max_tokens, A], router output when it must be widened
+    float *coef = nullptr, *coef_k = nullptr;
+    void *gu = nullptr, *hh = nullptr, *sh_h = nullptr, *sh_y = nullptr;  // act dtype
+    float *partial = nullptr;
+    void *group_ws = nullptr;
+    size_t group_ws_bytes = 0;
+    uint32_t *err = nullptr;       // [8]: router words 0..2, expert words 3..5
+    // host staging
+    void *pin_x = nullptr, *pin_y = nullptr;
+    uint32_t *pin_err = nullptr;
+    void *dev_x = nullptr, *dev_y = nullptr;
+    int64_t last_M = 0;
+};
+
+namespace {
+
+int check_desc(const strix_moe_layer_desc &d) {
+    const char *fn = "moe_layer_create";
+    SB_CHECK(d.d >= 32 && d.I >= 32 && d.E >= 1 && d.E <= 1023 && d.k >= 1 && d.k <= 32 && d.k <= d.E, fn, ": d = ", d.d, ", I = ", d.I,
+             ", E = ", d.E, ", k = ", d.k, " (E 1..1023, k 1..min(32, E))");
+    SB_CHECK(act_ok(d.act), fn, ": unsupported activation dtype ", d.act);
+    SB_CHECK(d.shared_mode >= 0 && d.shared_mode <= 2 && d.shared_coef_mode >= 0 && d.shared_coef_mode <= 1, fn, ": shared_mode ",
+             d.shared_mode, " / shared_coef_mode ", d.shared_coef_mode);
+    SB_CHECK(d.max_tokens >= 1 && d.max_tokens * (d.k + 1) <= (1 << 20), fn, ": max_tokens = ", d.max_tokens);
+    SB_CHECK(d.grouped_min_tokens >= 1, fn, ": grouped_min_tokens = ", d.grouped_min_tokens);
+    const bool gated = d.shared_mode != STRIX_SHARED_NONE && d.shared_coef_mode == STRIX_SHARED_COEF_SIGMOID;
+    const int64_t rows = d.E + (gated ? 1 : 0), Estack = d.E + (d.shared_mode == STRIX_SHARED_STACKED ? 1 : 0);
+    if (d.router_kind == STRIX_ROUTER_Q) {
+        SB_CHECK(bits_ok(d.router_bits) && d.router_q.q != nullptr && d.router_q.N == rows && d.router_q.K == d.d, fn,
+                 ": quantized router must be [", rows, ", ", d.d, "], got [", d.router_q.N, ", ", d.router_q.K, "] in ", d.router_bits, " bits");
+    } else {
+        SB_CHECK((d.router_kind == STRIX_ROUTER_F32 || d.router_kind == STRIX_ROUTER_BF16) && d.router_w != nullptr, fn,
+                 ": router_kind ", d.router_kind, " needs router_w");
+    }
+    if (d.experts_mixed) {
+        SB_CHECK(d.gate_up_mix.E == Estack && d.gate_up_mix.N == 2 * d.I && d.gate_up_mix.K == d.d, fn, ": gate_up_mix must be ", Estack,
+                 " experts of [", 2 * d.I, ", ", d.d, "]");
+        SB_CHECK(d.down_mix.E == Estack && d.down_mix.N == d.d && d.down_mix.K == d.I, fn, ": down_mix must be ", Estack, " experts of [",
+                 d.d, ", ", d.I, "]");
+    } else {
+        // strixite runtime/qweight.hpp:75-125: expert stacks are 4 or 5 bits.
+        SB_CHECK((d.gate_up_bits == 4 || d.gate_up_bits == 5) && (d.down_bits == 4 || d.down_bits == 5), fn, ": experts have ",
+                 d.gate_up_bits, "/", d.down_bits, " bits, expected 4 or 5 (or a per-expert format table)");
+        SB_CHECK(d.gate_up.N == Estack * 2 * d.I && d.gate_up.K == d.d, fn, ": gate_up must be [", Estack * 2 * d.I, ", ", d.d, "], got [",
+                 d.gate_up.N, ", ", d.gate_up.K, "]");
+        SB_CHECK(d.down.N == Estack * d.d && d.down.K == d.I, fn, ": down must be [", Estack * d.d, ", ", d.I, "], got [", d.down.N, ", ",
+                 d.down.K, "]");
+    }
+    if (d.shared_mode == STRIX_SHARED_SEPARATE) {
+        SB_CHECK(bits_ok(d.sh_gate_up_bits) && bits_ok(d.sh_down_bits), fn, ": shared expert bits ", d.sh_gate_up_bits, "/", d.sh_down_bits);
+        SB_CHECK(d.sh_gate_up.N == 2 * d.I && d.sh_gate_up.K == d.d && d.sh_down.N == d.d && d.sh_down.K == d.I, fn,
+                 ": shared expert must be [", 2 * d.I, ", ", d.d, "] and [", d.d, ", ", d.I, "]");
+    }
+    return 0;
+}
+
+int linear_any(int bits, const void *x, const strix_qview *w, void *y, int64_t M, int act, int out_act, void *stream) {
+    switch (bits) {
+        case 4: return strix_linear_q4(x, w, y, M, act, out_act, stream);
+        case 5: return strix_linear_q5(x, w, y, M, act, out_act, stream);
+        case 6: return strix_linear_q6(x, w, y, M, act, out_act, stream);
+        default: return strix_linear_q8(x, w, y, M, act, out_act, stream);
+    }
+}
+
+}  // namespace
+
+extern "C" {
+
+int strix_moe_layer_create(const strix_moe_layer_desc *desc, strix_moe_layer **out) {
+    SB_CHECK(desc != nullptr && out != nullptr, "moe_layer_create: null pointer");
+    SB_TRY(check_desc(*desc));
+    auto *L = new (std::nothrow) strix_moe_layer();
+    SB_CHECK(L != nullptr, "moe_layer_create: out of host memory");
+    L->d = *desc;
+    const auto &d = L->d;
+    L->gated = d.shared_mode != STRIX_SHARED_NONE && d.shared_coef_mode == STRIX_SHARED_COEF_SIGMOID;
+    L->router_rows = d.E + (L->gated ? 1 : 0);
+    L->Estack = d.E + (d.shared_mode == STRIX_SHARED_STACKED ? 1 : 0);
+    L->A = d.k + (d.shared_mode == STRIX_SHARED_STACKED ? 1 : 0);
+    const int64_t T = d.max_tokens, es = act_size(d.act);
+    int rc = 0;
+    auto a = [&](int r) { if (rc == 0) rc = r; };
+    a(dev_alloc(&L->logits, (size_t)(T * L->router_rows), "router logits"));
+    a(dev_alloc(&L->ids, (size_t)(T * L->A), "route ids"));
+    a(dev_alloc(&L->coef, (size_t)(T * L->A), "route coefficients"));
+    a(dev_alloc(&L->ids_k, (size_t)(T * d.k), "route ids (k)"));
+    a(dev_alloc(&L->coef_k, (size_t)(T * d.k), "route coefficients (k)"));
+    a(dev_alloc((char **)&L->gu, (size_t)(T * L->A * 2 * d.I * es), "gate_up outputs"));
+    a(dev_alloc((char **)&L->hh, (size_t)(T * L->A * d.I * es), "expert hidden"));
+    a(dev_alloc((char **)&L->sh_h, (size_t)(T * d.I * es), "shared hidden"));
+    a(dev_alloc((char **)&L->sh_y, (size_t)(T * d.d * es), "shared output"));
+    a(dev_alloc(&L->partial, (size_t)(T * L->A * d.d), "combine partials"));
+    L->group_ws_bytes = strix_moe_route_workspace_bytes(T, L->A, L->Estack);
+    a(L->group_ws_bytes == 0 ? STRIX_ERR_CHECK : 0);
+    a(dev_alloc((char **)&L->group_ws, L->group_ws_bytes, "grouping workspace"));
+    a(dev_alloc(&L->err, 8, "error words"));
+    a(dev_alloc((char **)&L->dev_x, (size_t)(T * d.d * es), "x staging"));
+    a(dev_alloc((char **)&L->dev_y, (size_t)(T * d.d * es), "y staging"));
+    if (rc == 0 && cudaMemset(L->err, 0, 32) != cudaSuccess) rc = STRIX_ERR_CUDA;
+    if (rc == 0 && cudaMallocHost(&L->pin_x, (size_t)(T * d.d * es)) != cudaSuccess) rc = STRIX_ERR_CUDA;
+    if (rc == 0 && cudaMallocHost(&L->pin_y, (size_t)(T * d.d * es)) != cudaSuccess) rc = STRIX_ERR_CUDA;
+    if (rc == 0 && cudaMallocHost(reinterpret_cast<void **>(&L->pin_err), 32) != cudaSuccess) rc = STRIX_ERR_CUDA;
+    if (rc != 0) {
+        if (rc == STRIX_ERR_CUDA && sb::last_error().empty()) sb::last_error() = "moe_layer_create: CUDA allocation failed";
+        strix_moe_layer_destroy(L);
+        return rc;
+    }
+    *out = L;
+    return 0;
+}
+
+void strix_moe_layer_destroy(strix_moe_layer *L) {
+    if (L == nullptr) return;
+    void *dev[] = {L->logits, L->ids, L->coef, L->ids_k, L->coef_k, L->gu, L->hh, L->sh_h, L->sh_y, L->partial, L->group_ws, L->err, L->dev_x, L->dev_y};
+    for (void *p : dev)
+        if (p) cudaFree(p);
+    if (L->pin_x) cudaFreeHost(L->pin_x);
+    if (L->pin_y) cudaFreeHost(L->pin_y);
+    if (L->pin_err) cudaFreeHost(L->pin_err);
+    delete L;
+}
+
+int strix_moe_layer_reset_errors(strix_moe_layer *L, void *stream) {
+    SB_CHECK(L != nullptr, "moe_layer_reset_errors: null layer");
+    SB_CUDA(cudaMemsetAsync(L->err, 0, 32, static_cast<cudaStream_t>(stream)), "clearing the error words");
+    return 0;
+}
+
+int strix_moe_layer_forward(strix_moe_layer *L, const void *x, int64_t M, void *y, void *stream) {
+    const char *fn = "moe_layer_forward";
+    SB_CHECK(L != nullptr && x != nullptr && y != nullptr, fn, ": null pointer");
+    const auto &d = L->d;
+    SB_CHECK(M >= 1 && M <= d.max_tokens, fn, ": ", M, " tokens, expected 1..", d.max_tokens);
+    auto st = static_cast<cudaStream_t>(stream);
+    const int act = d.act;
+    const int64_t E = d.E, A = L->A, R = L->router_rows;
+    uint32_t *router_err = L->err, *expert_err = L->err + 3;
+    L->last_M = M;
+
+    // 1. Router logits, FP32 [M, R]; row E (when gated) is the shared expert's gate.
+    if (d.router_kind == STRIX_ROUTER_Q) SB_TRY(linear_any(d.router_bits, x, &d.router_q, L->logits, M, act, STRIX_ACT_F32, stream));
+    else if (d.router_kind == STRIX_ROUTER_BF16)
+        SB_TRY(strix_linear_bf16w(x, static_cast<const uint16_t *>(d.router_w), L->logits, M, R, d.d, act, STRIX_ACT_F32, stream));
+    else SB_TRY(strix_linear_f32w(x, static_cast<const float *>(d.router_w), L->logits, M, R, d.d, act, STRIX_ACT_F32, stream));
+    if (d.router_bias != nullptr) {
+        add_bias_kernel<<<(unsigned)((M * E + 255) / 256), 256, 0, st>>>(L->logits, R, M, E, d.router_bias);
+        SB_LAUNCH_OK(fn, ": router bias");
+    }
+    // 2. Top-k + weights. The stacked shared expert takes slot k: gated through the router (the reference), or with
+    //    coefficient 1 written behind the router's k slots.
+    const bool stacked = d.shared_mode == STRIX_SHARED_STACKED;
+    if (stacked && !L->gated) {
+        SB_TRY(strix_moe_router(L->logits, R, M, E, d.k, nullptr, 0, 0, L->ids_k, L->coef_k, STRIX_ACT_F32, router_err, stream));
+        widen_rows_kernel<<<(unsigned)((M + 255) / 256), 256, 0, st>>>(L->ids_k, L->coef_k, L->ids, L->coef, M, d.k);
+        fill_shared_slot_kernel<<<(unsigned)((M + 255) / 256), 256, 0, st>>>(L->ids, L->coef, M, A, (int32_t)E);
+        SB_LAUNCH_OK(fn, ": shared slot");
+    } else {
+        SB_TRY(strix_moe_router(L->logits, R, M, E, d.k, stacked ? L->logits + E : nullptr, R, (int32_t)E, L->ids, L->coef, STRIX_ACT_F32,
+                                router_err, stream));
+    }
+    // 3. Routed experts: grouped from grouped_min_tokens on, per slot below.
+    if (M >= d.grouped_min_tokens) {
+        SB_TRY(strix_moe_group_routes(L->ids, M, A, L->Estack, L->group_ws, L->group_ws_bytes, expert_err, stream));
+        if (d.experts_mixed) {
+            SB_TRY(strix_linear_qmix_experts_gather_grouped(x, &d.gate_up_mix, L->group_ws, L->group_ws_bytes, M, A, L->gu, act, d.math, stream));
+            SB_TRY(strix_swiglu(L->gu, L->hh, M * A, d.I, act, stream));
+            SB_TRY(strix_linear_qmix_experts_combine_grouped(L->hh, &d.down_mix, L->ids, L->coef, L->group_ws, L->group_ws_bytes, L->partial, M,
+                                                             A, y, act, d.math, stream));
+        } else {
+            auto gather = d.gate_up_bits == 4 ? strix_linear_q4_experts_gather_grouped : strix_linear_q5_experts_gather_grouped;
+            auto combine = d.down_bits == 4 ? strix_linear_q4_experts_combine_grouped : strix_linear_q5_experts_combine_grouped;
+            SB_TRY(gather(x, &d.gate_up, L->Estack, L->group_ws, L->group_ws_bytes, M, A, L->gu, act, d.math, stream));
+            SB_TRY(strix_swiglu(L->gu, L->hh, M * A, d.I, act, stream));
+            SB_TRY(combine(L->hh, &d.down, L->Estack, L->ids, L->coef, L->group_ws, L->group_ws_bytes, L->partial, M, A, y, act, d.math, stream));
+        }
+    } else if (d.experts_mixed) {
+        SB_TRY(strix_linear_qmix_experts_gather_swiglu(x, &d.gate_up_mix, L->ids, M, A, L->hh, act, expert_err, stream));
+        SB_TRY(strix_linear_qmix_experts_combine(L->hh, &d.down_mix, L->ids, L->coef, M, A, y, act, expert_err, stream));
+    } else {
+        auto gather = d.gate_up_bits == 4 ? strix_linear_q4_experts_gather_swiglu : strix_linear_q5_experts_gather_swiglu;
+        auto combine = d.down_bits == 4 ? strix_linear_q4_experts_combine : strix_linear_q5_experts_combine;
+        SB_TRY(gather(x, &d.gate_up, L->Estack, L->ids, M, A, L->hh, act, expert_err, stream));
+        SB_TRY(combine(L->hh, &d.down, L->Estack, L->ids, L->coef, M, A, y, act, expert_err, stream));
+    }
+    // 4. The shared expert as dense projections, then y += sigmoid(gate) * s (or y += s when always on).
+    if (d.shared_mode == STRIX_SHARED_SEPARATE) {
+        SB_TRY(linear_any(d.sh_gate_up_bits, x, &d.sh_gate_up, L->gu, M, act, act, stream));
+        SB_TRY(strix_swiglu(L->gu, L->sh_h, M, d.I, act, stream));
+        SB_TRY(linear_any(d.sh_down_bits, L->sh_h, &d.sh_down, L->sh_y, M, act, act, stream));
+        if (L->gated) SB_TRY(strix_moe_shared_add(y, L->sh_y, L->logits + E, R, M, d.d, (uint32_t)E, act, router_err, stream));
+        else SB_TRY(strix_residual_add(y, L->sh_y, M * d.d, act, stream));
+    }
+    return 0;
+}
+
+int strix_moe_layer_forward_host(strix_moe_layer *L, const void *x_host, int64_t M, void *y_host, void *stream) {
+    const char *fn = "moe_layer_forward_host";
+    SB_CHECK(L != nullptr && x_host != nullptr && y_host != nullptr, fn, ": null pointer");
+    SB_CHECK(M >= 1 && M <= L->d.max_tokens, fn, ": ", M, " tokens, expected 1..", L->d.max_tokens);
+    auto st = static_cast<cudaStream_t>(stream);
+    const size_t bytes = (size_t)(M * L->d.d * act_size(L->d.act));
+    std::memcpy(L->pin_x, x_host, bytes);
+    SB_CUDA(cudaMemcpyAsync(L->dev_x, L->pin_x, bytes, cudaMemcpyHostToDevice, st), fn, ": x to the device");
+    SB_TRY(strix_moe_layer_forward(L, L->dev_x, M, L->dev_y, stream));
+    SB_CUDA(cudaMemcpyAsync(L->pin_y, L->dev_y, bytes, cudaMemcpyDeviceToHost, st), fn, ": y to the host");
+    SB_CUDA(cudaMemcpyAsync(L->pin_err, L->err, 24, cudaMemcpyDeviceToHost, st), fn, ": error words to the host");
+    SB_CUDA(cudaStreamSynchronize(st), fn, ": waiting for the layer");
+    std::memcpy(y_host, L->pin_y, bytes);
+    SB_TRY(strix_report_router_error(L->pin_err, "moe layer router"));
+    SB_TRY(strix_report_expert_error(L->pin_err + 3, "moe layer experts"));
+    return 0;
+}
+
+int strix_moe_stack_forward(strix_moe_layer *const *layers, int64_t n_layers, void *x, int64_t M, void *tmp, void *stream) {
+    SB_CHECK(layers != nullptr && x != nullptr && tmp != nullptr && n_layers >= 1, "moe_stack_forward: null pointer or no layers");
+    for (int64_t l = 0; l < n_layers; ++l) {
+        SB_CHECK(layers[l] != nullptr && layers[l]->d.d == layers[0]->d.d && layers[l]->d.act == layers[0]->d.act,
+                 "moe_stack_forward: layer ", l, " is null or differs in hidden size / dtype");
+        SB_TRY(strix_moe_layer_forward(layers[l], x, M, tmp, stream));
+        SB_TRY(strix_residual_add(x, tmp, M * layers[l]->d.d, layers[l]->d.act, stream));
+    }
+    return 0;
+}
+
+const void *strix_moe_layer_probe(strix_moe_layer *L, const char *name) {
+    if (L == nullptr || name == nullptr) return nullptr;
+    if (!std::strcmp(name, "router_logits")) return L->logits;
+    if (!std::strcmp(name, "router_ids")) return L->ids;
+    if (!std::strcmp(name, "router_coef")) return L->coef;
+    if (!std::strcmp(name, "experts_h")) return L->hh;
+    if (!std::strcmp(name, "shared_h")) return L->sh_h;
+    if (!std::strcmp(name, "shared_y")) return L->sh_y;
+    if (!std::strcmp(name, "err")) return L->err;
+    if (!std::strcmp(name, "group_ws")) return L->group_ws;
+    return nullptr;
+}
+
+}  // extern "C"
