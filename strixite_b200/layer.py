@@ -119,14 +119,21 @@ class MoeLayer:
             "router_coef": ((M, self.A), torch.float32), "experts_h": ((M, self.A, self.I), K._dtype(self.act)),
             "shared_h": ((M, self.I), K._dtype(self.act)), "shared_y": ((M, self.d), K._dtype(self.act)), "err": ((6,), torch.int32),
         }
+        bf16 = shapes[name][1] == torch.bfloat16
         shape, dt = shapes[name]
-        out = torch.empty(shape, dtype=dt, device="cuda")
         torch.cuda.current_stream().synchronize()
-        n = out.numel() * out.element_size()
-        rc = torch.cuda.cudart().cudaMemcpy(out.data_ptr(), p, n, 3)  # cudaMemcpyDeviceToDevice
-        if int(rc) != 0:
-            raise StrixError("MoeLayer.probe: cudaMemcpy failed (%s)" % rc)
-        return out
+        out = torch.as_tensor(_DevArray(p, shape, dt), device="cuda").clone()
+        return out.view(torch.bfloat16) if bf16 else out
+
+
+class _DevArray:
+    """A device buffer of the library seen through __cuda_array_interface__ (read by torch.as_tensor, then cloned)."""
+
+    _TYPESTR = {torch.float32: "<f4", torch.int32: "<i4", torch.bfloat16: "<i2"}
+
+    def __init__(self, ptr, shape, dtype):
+        self._bf16 = dtype == torch.bfloat16
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": self._TYPESTR[dtype], "data": (int(ptr), False), "version": 3}
 
 
 def stack_forward(layers, x, tmp=None, stream=None):
