@@ -5,7 +5,7 @@
  *   - plain pointers and sizes only; device pointers unless the name says host;
  *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream);
  *   - everything is enqueued asynchronously; nothing allocates, synchronizes or keeps state between calls, except
- *     the check_*_error readers (which copy 3 words back, so they synchronize), the strix_layer_* session object
+ *     the check_*_error readers (which copy 3 words back, so they synchronize), the strix_moe_layer_* session object
  *     and the function whose comment says otherwise;
  *   - return value: 0 = enqueued; 1 = an argument check failed; 2 = a CUDA call failed. strix_last_error() gives
  *     the message of the calling thread's last failure ("func (file:line): check `cond` failed: ...");
@@ -216,6 +216,8 @@ typedef struct strix_moe_layer_desc {
     int64_t max_tokens;
     int64_t grouped_min_tokens; /* the grouped path runs from this many tokens (reference: 6, runtime/qwen4exp.hpp:266) */
     int math;                   /* STRIX_MATH_* of the grouped path */
+    int decode_impl;            /* forwards of <= 8 tokens: 0 = the fused single-kernel path where the shapes allow it,
+                                 * 1 = the per-function kernels in the reference's sequence */
 } strix_moe_layer_desc;
 
 typedef struct strix_moe_layer strix_moe_layer;

@@ -3,6 +3,7 @@
 // Nothing here computes: it validates, owns workspaces, picks the per-slot or grouped experts path and enqueues.
 #include "common.cuh"
 
+#include "decode_fused.cuh"
 #include "strixite_b200.h"
 
 #include <cstring>
@@ -65,6 +66,11 @@ struct strix_moe_layer {
     uint32_t *pin_err = nullptr;
     void *dev_x = nullptr, *dev_y = nullptr;
     int64_t last_M = 0;
+    // the fused decode kernel's scratch and plan
+    uint8_t *hrec = nullptr;
+    uint32_t *sync = nullptr;
+    bool fused_ok = false;
+    sb::DecodeParams plan{};
 };
 
 namespace {
@@ -152,6 +158,30 @@ int strix_moe_layer_create(const strix_moe_layer_desc *desc, strix_moe_layer **o
     a(dev_alloc(&L->err, 8, "error words"));
     a(dev_alloc((char **)&L->dev_x, (size_t)(T * d.d * es), "x staging"));
     a(dev_alloc((char **)&L->dev_y, (size_t)(T * d.d * es), "y staging"));
+    {
+        // Fused decode kernel: its shared-memory plan for up to 8 tokens, the h records and the barrier words.
+        sb::DecodeParams &p = L->plan;
+        const int64_t Mf = T < 8 ? T : 8;
+        p.M = (int)Mf, p.d = (int)d.d, p.I = (int)d.I, p.E = (int)d.E, p.k = (int)d.k, p.A = (int)L->A, p.R = (int)L->router_rows,
+        p.Estack = (int)L->Estack, p.act = d.act, p.shared_mode = d.shared_mode, p.gated = L->gated ? 1 : 0;
+        int bits_gu = d.experts_mixed ? 8 : d.gate_up_bits, bits_dn = d.experts_mixed ? 8 : d.down_bits;
+        int64_t minG = d.experts_mixed ? (d.gate_up_mix.G < d.down_mix.G ? d.gate_up_mix.G : d.down_mix.G) : (d.gate_up.G < d.down.G ? d.gate_up.G : d.down.G);
+        bool aligned = true;
+        auto al = [&](const void *q) { aligned = aligned && sb::aligned16(q); };
+        if (d.experts_mixed) al(d.gate_up_mix.scale), al(d.gate_up_mix.minv), al(d.down_mix.scale), al(d.down_mix.minv);
+        else al(d.gate_up.scale), al(d.gate_up.minv), al(d.down.scale), al(d.down.minv);
+        if (d.shared_mode == STRIX_SHARED_SEPARATE) {
+            bits_gu = d.sh_gate_up_bits > bits_gu ? d.sh_gate_up_bits : bits_gu, bits_dn = d.sh_down_bits > bits_dn ? d.sh_down_bits : bits_dn;
+            minG = d.sh_gate_up.G < minG ? d.sh_gate_up.G : minG, minG = d.sh_down.G < minG ? d.sh_down.G : minG;
+            al(d.sh_gate_up.scale), al(d.sh_gate_up.minv), al(d.sh_down.scale), al(d.sh_down.minv), al(d.sh_gate_up.q), al(d.sh_down.q);
+        }
+        L->fused_ok = rc == 0 && aligned && d.decode_impl == 0 && sb::decode_fused_plan(p, bits_gu, bits_dn, (int)minG) != 0;
+        if (L->fused_ok) {
+            a(dev_alloc(&L->hrec, (size_t)((Mf * L->A + Mf) * p.hrec_bytes), "fused decode h records"));
+            a(dev_alloc(&L->sync, 128, "fused decode barrier words"));
+            if (rc == 0 && cudaMemset(L->sync, 0, 512) != cudaSuccess) rc = STRIX_ERR_CUDA;
+        }
+    }
     if (rc == 0 && cudaMemset(L->err, 0, 32) != cudaSuccess) rc = STRIX_ERR_CUDA;
     if (rc == 0 && cudaMallocHost(&L->pin_x, (size_t)(T * d.d * es)) != cudaSuccess) rc = STRIX_ERR_CUDA;
     if (rc == 0 && cudaMallocHost(&L->pin_y, (size_t)(T * d.d * es)) != cudaSuccess) rc = STRIX_ERR_CUDA;
@@ -167,7 +197,7 @@ int strix_moe_layer_create(const strix_moe_layer_desc *desc, strix_moe_layer **o
 
 void strix_moe_layer_destroy(strix_moe_layer *L) {
     if (L == nullptr) return;
-    void *dev[] = {L->logits, L->ids, L->coef, L->ids_k, L->coef_k, L->gu, L->hh, L->sh_h, L->sh_y, L->partial, L->group_ws, L->err, L->dev_x, L->dev_y};
+    void *dev[] = {L->logits, L->ids, L->coef, L->ids_k, L->coef_k, L->gu, L->hh, L->sh_h, L->sh_y, L->partial, L->group_ws, L->err, L->dev_x, L->dev_y, L->hrec, L->sync};
     for (void *p : dev)
         if (p) cudaFree(p);
     if (L->pin_x) cudaFreeHost(L->pin_x);
@@ -179,6 +209,7 @@ void strix_moe_layer_destroy(strix_moe_layer *L) {
 int strix_moe_layer_reset_errors(strix_moe_layer *L, void *stream) {
     SB_CHECK(L != nullptr, "moe_layer_reset_errors: null layer");
     SB_CUDA(cudaMemsetAsync(L->err, 0, 32, static_cast<cudaStream_t>(stream)), "clearing the error words");
+    if (L->sync != nullptr) SB_CUDA(cudaMemsetAsync(L->sync, 0, 16, static_cast<cudaStream_t>(stream)), "clearing the barrier words");
     return 0;
 }
 
@@ -193,6 +224,24 @@ int strix_moe_layer_forward(strix_moe_layer *L, const void *x, int64_t M, void *
     uint32_t *router_err = L->err, *expert_err = L->err + 3;
     L->last_M = M;
 
+    if (L->fused_ok && M <= 8) {
+        // Decode / verify: the whole sublayer in one persistent kernel.
+        sb::DecodeParams p = L->plan;
+        p.M = (int)M, p.x = x, p.y = y;
+        p.router_kind = d.router_kind, p.router_bits = d.router_bits, p.router_w = d.router_w, p.router_q = d.router_q, p.router_bias = d.router_bias;
+        if (d.experts_mixed) {
+            p.gate_up = sb::StackView{d.gate_up_mix.q, d.gate_up_mix.scale, d.gate_up_mix.minv, d.gate_up_mix.bits, d.gate_up_mix.q_off, 0, d.gate_up_mix.N, d.gate_up_mix.K, d.gate_up_mix.G};
+            p.down = sb::StackView{d.down_mix.q, d.down_mix.scale, d.down_mix.minv, d.down_mix.bits, d.down_mix.q_off, 0, d.down_mix.N, d.down_mix.K, d.down_mix.G};
+        } else {
+            p.gate_up = sb::StackView{d.gate_up.q, d.gate_up.scale, d.gate_up.minv, nullptr, nullptr, d.gate_up_bits, 2 * d.I, d.d, d.gate_up.G};
+            p.down = sb::StackView{d.down.q, d.down.scale, d.down.minv, nullptr, nullptr, d.down_bits, d.d, d.I, d.down.G};
+        }
+        p.sh_gate_up_bits = d.sh_gate_up_bits, p.sh_down_bits = d.sh_down_bits, p.sh_gate_up = d.sh_gate_up, p.sh_down = d.sh_down;
+        p.logits = L->logits, p.ids = L->ids, p.coef = L->coef, p.hh = L->hh, p.sh_h = L->sh_h, p.hrec = L->hrec, p.err = L->err, p.sync = L->sync;
+        // the plan was made for min(max_tokens, 8) tokens; fewer tokens only leave more room
+        SB_TRY(sb::decode_fused_launch(fn, p, st));
+        return 0;
+    }
     // 1. Router logits, FP32 [M, R]; row E (when gated) is the shared expert's gate.
     if (d.router_kind == STRIX_ROUTER_Q) SB_TRY(linear_any(d.router_bits, x, &d.router_q, L->logits, M, act, STRIX_ACT_F32, stream));
     else if (d.router_kind == STRIX_ROUTER_BF16)
@@ -288,6 +337,7 @@ const void *strix_moe_layer_probe(strix_moe_layer *L, const char *name) {
     if (!std::strcmp(name, "shared_y")) return L->sh_y;
     if (!std::strcmp(name, "err")) return L->err;
     if (!std::strcmp(name, "group_ws")) return L->group_ws;
+    if (!std::strcmp(name, "fused_sync")) return L->sync;
     return nullptr;
 }
 

@@ -23,7 +23,7 @@ class _Desc(C.Structure):
         ("experts_mixed", C.c_int), ("gate_up_bits", C.c_int), ("down_bits", C.c_int),
         ("gate_up", QView), ("down", QView), ("gate_up_mix", QMixView), ("down_mix", QMixView),
         ("sh_gate_up_bits", C.c_int), ("sh_down_bits", C.c_int), ("sh_gate_up", QView), ("sh_down", QView),
-        ("max_tokens", C.c_int64), ("grouped_min_tokens", C.c_int64), ("math", C.c_int),
+        ("max_tokens", C.c_int64), ("grouped_min_tokens", C.c_int64), ("math", C.c_int), ("decode_impl", C.c_int),
     ]
 
 
@@ -53,7 +53,7 @@ class MoeLayer:
     """
 
     def __init__(self, d, I, E, k, act, router, gate_up, down, shared=None, shared_coef="sigmoid", sh_gate_up=None, sh_down=None,
-                 router_bias=None, max_tokens=8, grouped_min_tokens=kGroupedMinTokens, math=K.MoeMath.F32):
+                 router_bias=None, max_tokens=8, grouped_min_tokens=kGroupedMinTokens, math=K.MoeMath.F32, decode_impl=0):
         self._keep = [router, gate_up, down, sh_gate_up, sh_down, router_bias]  # the views must outlive the layer
         self.d, self.I, self.E, self.k, self.act, self.max_tokens = d, I, E, k, K.Act(act), max_tokens
         self.A = k + (1 if shared == "stacked" else 0)
@@ -78,7 +78,7 @@ class MoeLayer:
             ds.gate_up_bits, ds.down_bits, ds.gate_up, ds.down = gate_up.bits, down.bits, gate_up.view(), down.view()
         if shared == "separate":
             ds.sh_gate_up_bits, ds.sh_down_bits, ds.sh_gate_up, ds.sh_down = sh_gate_up.bits, sh_down.bits, sh_gate_up.view(), sh_down.view()
-        ds.max_tokens, ds.grouped_min_tokens, ds.math = max_tokens, grouped_min_tokens, int(math)
+        ds.max_tokens, ds.grouped_min_tokens, ds.math, ds.decode_impl = max_tokens, grouped_min_tokens, int(math), int(decode_impl)
         self._desc = ds
         h = C.c_void_p()
         call("strix_moe_layer_create", C.byref(ds), C.byref(h))
@@ -117,7 +117,7 @@ class MoeLayer:
         shapes = {
             "router_logits": ((M, self.router_rows), torch.float32), "router_ids": ((M, self.A), torch.int32),
             "router_coef": ((M, self.A), torch.float32), "experts_h": ((M, self.A, self.I), K._dtype(self.act)),
-            "shared_h": ((M, self.I), K._dtype(self.act)), "shared_y": ((M, self.d), K._dtype(self.act)), "err": ((6,), torch.int32),
+            "shared_h": ((M, self.I), K._dtype(self.act)), "shared_y": ((M, self.d), K._dtype(self.act)), "err": ((6,), torch.int32), "fused_sync": ((128,), torch.int32),
         }
         bf16 = shapes[name][1] == torch.bfloat16
         shape, dt = shapes[name]

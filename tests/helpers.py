@@ -4,7 +4,7 @@ import numpy as np
 
 import oracle
 
-BF16_ULP = 2.0 ** -8  # one BF16 step relative to a value's magnitude (8 significand bits)
+BF16_ULP = 2.0 ** -7  # the largest relative size of one BF16 step (just above a power of two; 8 significand bits)
 
 
 def rel_err_rows(y, ref):
@@ -14,6 +14,16 @@ def rel_err_rows(y, ref):
     ref = np.asarray(ref, np.float64).reshape(-1, ref.shape[-1])
     den = np.maximum(np.abs(ref).max(axis=1), 1e-30)
     return (np.abs(y - ref).max(axis=1) / den).max()
+
+
+def bf16_rows_close(y, ref, tol):
+    """BF16 outputs: |y - ref| <= tol * max|ref| of the row + one BF16 step of the reference element (the two sides may
+    round a near-tie differently). Returns the worst excess ratio (<= 1 passes)."""
+    y = np.asarray(y, np.float64).reshape(-1, y.shape[-1])
+    ref = np.asarray(ref, np.float64).reshape(-1, ref.shape[-1])
+    rowmax = np.maximum(np.abs(ref).max(axis=1, keepdims=True), 1e-30)
+    ulp = 2.0 ** (np.floor(np.log2(np.maximum(np.abs(ref), 1e-30))) - 7)
+    return (np.abs(y - ref) / (tol * rowmax + ulp)).max()
 
 
 def to_np_act(t):
@@ -92,7 +102,7 @@ def make_layer(seed, d, I, E, k, G=128, router="f32", shared="stacked", shared_c
     return L
 
 
-def gpu_layer(L, act, max_tokens, grouped_min_tokens=6, math=0):
+def gpu_layer(L, act, max_tokens, grouped_min_tokens=6, math=0, decode_impl=0):
     """The device twin of a make_layer() dict."""
     import torch
 
@@ -112,4 +122,4 @@ def gpu_layer(L, act, max_tokens, grouped_min_tokens=6, math=0):
         kw["router_bias"] = torch.from_numpy(L["router_bias"]).cuda()
     return sb.MoeLayer(L["d"], L["I"], L["E"], L["k"], act, router, upload_stack(L["gate_up"]), upload_stack(L["down"]),
                        shared=L.get("shared"), shared_coef=L.get("shared_coef", "sigmoid"), max_tokens=max_tokens,
-                       grouped_min_tokens=grouped_min_tokens, math=math, **kw)
+                       grouped_min_tokens=grouped_min_tokens, math=math, decode_impl=decode_impl, **kw)
