@@ -1,17 +1,20 @@
 // The whole MoE sublayer for a handful of tokens (decode, speculative verify: M <= 8) as ONE persistent kernel.
 //
 // A decode layer moves ~20-100 MB of packed expert weights exactly once and does almost no arithmetic, so the design
-// is a weight-streaming machine: one CTA per SM, a producer warp that keeps a deep ring of shared-memory stages full
-// with bulk asynchronous copies (cp.async.bulk + mbarrier transaction counts: slices of packed code rows, their BF16
-// scales and minima), and sixteen consumer warps, one stage each, that turn the staged nibbles into dot products.
+// is a weight-streaming machine: one CTA per SM, twelve warps, each running its own software pipeline of asynchronous
+// 16-byte copies (cp.async.cg, L2 -> shared memory, no registers) into a private ring of padded shared-memory stages,
+// and turning the staged nibbles into dot products. (Bulk-copy engines were measured first: one cp.async.bulk per row
+// slice costs ~100 cycles of issue time whatever its size, which capped a CTA near 5 B/clk; rows need padding for
+// conflict-free reads, so they cannot be fetched as one large contiguous bulk copy either.)
 // The dots run on the tensor cores as a data-movement trick, not as a GEMM: mma.sync m16n8k16 takes 16 weight rows x
-// 16 codes against up to 8 token columns, so one unpack of a weight word (lop3 into BF16 "128 + code", exact) serves
-// every token and the CUDA cores only unpack. FP32 activations are split into two BF16 planes (x = hi + lo, products
-// exact, FP32 accumulate); the "+128" offset and the group minimum fold into one FMA per quantization group:
-// s * acc + (m - 128 s) * sum(hi + lo). Each distinct active expert is streamed once however many tokens chose it.
+// 16 codes against 8 columns, so one unpack of a weight word (lop3 into BF16 "128 + code", exact) serves every token
+// and the CUDA cores only unpack. FP32 activations are split into two BF16 planes (x = hi + lo, products exact, FP32
+// accumulate) that sit side by side in the 8 MMA columns (4 tokens x 2 planes per pass); the "+128" offset and the
+// group minimum fold into one FMA per quantization group: s * acc + (m - 128 s) * sum(plane). Each distinct active
+// expert is streamed once however many tokens chose it.
 //
 // Phases (two grid barriers; the CTAs are co-resident by a cooperative launch):
-//   0  x -> FP32 copy and permuted BF16 planes in shared memory, per-chunk sums
+//   0  x -> FP32 copy and permuted BF16 planes in shared memory, per-plane chunk sums
 //   1  router logits [M, R]: two warps per router row, FP32 FMA, weights straight from global memory
 //   -- barrier --
 //   2  every CTA: top-k + weights for the M tokens and the distinct-expert groups; then gate/up tiles: 8 gate + 8 up
@@ -23,9 +26,8 @@
 // The separate (dense) shared expert is one more group whose tokens are all M; its part is rounded and added as the
 // reference's moe_shared_add does. Summation orders are fixed: the output is bit-reproducible.
 //
-// Every wait (mbarrier, grid barrier) is bounded: on expiry the CTA raises the abort word and all CTAs leave; the
-// host sees the expert error words {2, 0xdec000 | 0x100 | wait id, block} (wait ids: 1/2 producer/consumer of phase 2,
-// 3/4 of phase 3, 5 a grid barrier).
+// The only waits that depend on other CTAs are the two grid barriers; they are bounded: on expiry the CTA raises the
+// abort word, all CTAs leave and the host sees the expert error words {2, 0xdec000 | code, block}.
 #include "common.cuh"
 
 #include "decode_fused.cuh"
@@ -35,55 +37,32 @@ namespace {
 
 using namespace sb;
 
-constexpr int CW = 12;                     // consumer warps (13 warps allocate registers as 16: 128 per thread)
-constexpr int kThreads = 32 * (CW + 1);    // warp 0 produces
+constexpr int CW = 12;                     // warps; every warp streams and consumes its own stages
+constexpr int kThreads = 32 * CW;
 constexpr int kMaxTok = 8;
 constexpr int kMaxGroups = 96;
 constexpr int kMaxSlots = kMaxGroups - 1;
-constexpr int kMaxStages = 48;
+constexpr int kMaxDepth = 4;               // stages per warp
 constexpr uint32_t kSpinLimit = 1u << 22;  // polls before a wait gives up (each poll is tens of ns)
 
 // ---- PTX wrappers ----------------------------------------------------------------------------------------------
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
-__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+// 16-byte asynchronous copy global -> shared through L2 (both addresses 16-byte aligned).
+__device__ __forceinline__ void cp_async16(void *dst, const void *src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
 }
-__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// Bounded wait; false = gave up (or another thread of the CTA already did).
-// `where` identifies the wait in the error words should it expire.
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int where = 0) {
-    for (uint32_t i = 0; i < kSpinLimit; ++i) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 255u) == 0u && *abort_flag) return false;
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+// Waits until at most `pending` of this thread's committed copy groups are still in flight.
+__device__ __forceinline__ void cp_async_wait(int pending) {
+    switch (pending) {
+        case 0: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
+        case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
+        case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
+        default: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
     }
-    if (*abort_flag == 0) *abort_flag = 0x100 | where;
-    return false;
 }
-// Global -> shared bulk copy; size a multiple of 16 bytes, both addresses 16-byte aligned.
-__device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst)),
-                 "l"(src), "r"(bytes), "r"(smem_u32(bar))
-                 : "memory");
-}
-__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async;" ::: "memory"); }
 __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
@@ -123,8 +102,6 @@ struct Group {  // one distinct active expert with both projections resolved
 };
 
 struct Smem {
-    uint64_t full_g[kMaxStages], empty_g[kMaxStages];  // phase 2 ring
-    uint64_t full_d[kMaxStages], empty_d[kMaxStages];  // phase 3 ring
     Group groups[kMaxGroups];
     int32_t ids[kMaxSlots + 1];
     float coef[kMaxSlots + 1];
@@ -132,7 +109,7 @@ struct Smem {
     float gate[kMaxTok];         // the separate shared expert's coefficient per token
     float red[2][CW][32][8];     // team exchange (phase 2) / cross-warp partial tiles (phase 3): [pass][4] per lane
     float red_sh[2][32][8];      // phase 3: the separate shared expert's tile, kept apart for its own rounding
-    float rpart[CW + 1][kMaxTok];  // phase 1: half-row partial logits
+    float rpart[CW][kMaxTok];  // phase 1: half-row partial logits
     int leaders_before[CW + 2];
     int n_groups, col_max, abort_flag;
     uint32_t failed_mask;        // tokens the router failed (non-finite logits): NaN rows
@@ -207,7 +184,7 @@ struct Unit {
 // Columns: BF16 activations use one pass, column n = token n. FP32 activations pack a token's two BF16 planes side by
 // side - column n = token (n & 3) + 4 * pass, plane n >> 2 - so that one MMA covers both planes of up to 4 tokens.
 // Independent accumulators per MMA of a unit keep the tensor pipe from waiting on its own results.
-template <int BITS, int NP>
+template <int BITS, int NP, int NCH>  // NCH: 32-code chunks per group when known at compile time (4 = groups of 128), 0 = n_chunks
 __device__ __forceinline__ void group_dot(const uint8_t *rowA, const uint8_t *rowB, int Ks, const uint8_t *const (&xb)[NP], int u0, int n_chunks,
                                           int c, float sA, float mA, float sB, float mB, const float (&xs)[NP][2], float (&tot)[NP][4]) {
     float a0[NP][4], a1[NP][4], h0[BITS == 8 ? NP : 1][4], h1[BITS == 8 ? NP : 1][4];
@@ -218,8 +195,8 @@ __device__ __forceinline__ void group_dot(const uint8_t *rowA, const uint8_t *ro
             a0[p][i] = 0.f, a1[p][i] = 0.f;
             if (BITS == 8) h0[p][i] = 0.f, h1[p][i] = 0.f;
         }
-#pragma unroll 2
-    for (int q = 0; q < n_chunks; ++q) {
+#pragma unroll
+    for (int q = 0; q < (NCH ? NCH : n_chunks); ++q) {
         const int u = u0 + 4 * q + c;  // a 32-code chunk is 4 units, one per lane of the quad
         Unit<BITS> a, b;
         a.load(rowA, Ks, u);
@@ -519,13 +496,62 @@ __device__ void build_groups(const DecodeParams &p, Smem &sm, int tid) {
 
 // ---- the fused kernel ------------------------------------------------------------------------------------------------
 
-// The ring of a phase: consumer warp cw owns the slots [cw * depth, (cw + 1) * depth); the n-th stage it consumes sits
-// in slot cw * depth + n % depth with mbarrier parity (n / depth) & 1. Stages are numbered it = 0, 1, .. in the order
-// the producer issues them; stage it belongs to warp it % active. A slot is always consumed by the same warp, in order,
-// so a parity wait can never be satisfied by an older phase.
-struct Ring {
-    int active, depth;
-};
+// The copies of one gate/up stage: K slice h of the tile's 16 rows (8 gate rows, then the matching 8 up rows) into padded
+// rows of the stage, and the tile's four scale / min runs (8 rows x all groups each). A half warp walks a row.
+__device__ __forceinline__ void gu_issue(const DecodeParams &p, const Group &grp, int jb, int h, int nk, uint8_t *st, int rs, int sc_off,
+                                         int sc_bytes, int lane) {
+    const int d = p.d, I = p.I, Ks = d / nk;
+    const int bits = grp.bits[0], gpr = d / grp.G[0];
+    const int rb = (int)row_bytes(bits, d), lo_b = slice_lo_bytes(bits, Ks), hi_b = slice_hi_bytes(bits, Ks);
+    const int lo_p = lo_b / 16, ppr = lo_p + hi_b / 16;  // 16-byte pieces per row slice
+    // a half warp walks a row: rows (lane >> 4), + 2, ..; gate rows 0..7 then up rows 8..15 (I rows further)
+    const uint8_t *src = grp.rows[0] + ((int64_t)jb * 8 + (lane >> 4)) * rb;
+    uint8_t *dst = st + (lane >> 4) * rs;
+    const int pc0 = lane & 15, hi_src = slice_lo_bytes(bits, d) + h * hi_b - lo_b;  // high-plane pieces: offset from pc * 16
+#pragma unroll 1
+    for (int half = 0; half < 2; ++half) {
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            for (int pc = pc0; pc < ppr; pc += 16) cp_async16(dst + pc * 16, src + (pc < lo_p ? h * lo_b : hi_src) + pc * 16);
+            src += 2 * rb, dst += 2 * rs;
+        }
+        src += (int64_t)(I - 8) * rb;
+    }
+    const int rp = gpr;  // 16-byte pieces per run of 8 rows x gpr groups x 2 bytes
+    for (int i = lane; i < 4 * rp; i += 32) {
+        const int which = i / rp, pc = i - which * rp;  // 0 gate scale, 1 gate min, 2 up scale, 3 up min
+        const int r0 = (which & 2) ? I + jb * 8 : jb * 8;
+        const uint8_t *src = reinterpret_cast<const uint8_t *>(((which & 1) ? grp.minv[0] : grp.scale[0]) + (int64_t)r0 * gpr);
+        cp_async16(st + sc_off + which * sc_bytes + pc * 16, src + pc * 16);
+    }
+}
+
+// The copies of one down stage: 16 consecutive output rows of the group's expert, their scale / min runs, and the h records
+// of the tokens routed to it (ascending token order).
+__device__ __forceinline__ void dn_issue(const DecodeParams &p, const Group &grp, int nb, uint8_t *st, int rs, int sc_off, int sc_bytes,
+                                         int col_off, int lane) {
+    const int I = p.I, M = p.M, A = p.A;
+    const int bits = grp.bits[1], gpr = I / grp.G[1];
+    const int rb = (int)row_bytes(bits, I), ppr = rb / 16;
+    for (int r = lane >> 4; r < 16; r += 2) {
+        const uint8_t *src = grp.rows[1] + ((int64_t)nb * 16 + r) * rb;
+        for (int pc = lane & 15; pc < ppr; pc += 16) cp_async16(st + r * rs + pc * 16, src + pc * 16);
+    }
+    const int rp = 2 * gpr;  // 16 rows x gpr groups x 2 bytes
+    for (int i = lane; i < 2 * rp; i += 32) {
+        const int which = i / rp, pc = i - which * rp;
+        const uint8_t *src = reinterpret_cast<const uint8_t *>((which ? grp.minv[1] : grp.scale[1]) + (int64_t)nb * 16 * gpr);
+        cp_async16(st + sc_off + which * sc_bytes + pc * 16, src + pc * 16);
+    }
+    const int cp_n = p.hrec_bytes / 16;
+    int ci = 0;
+    for (uint32_t mk = grp.mask; mk; mk &= mk - 1, ++ci) {
+        const int m = __ffs(mk) - 1;
+        const int slot_i = grp.expert == -2 ? M * A + m : m * A + grp.slot_a[m];
+        const uint8_t *src = p.hrec + (int64_t)slot_i * p.hrec_bytes;
+        for (int pc = lane; pc < cp_n; pc += 32) cp_async16(st + col_off + ci * p.hrec_bytes + pc * 16, src + pc * 16);
+    }
+}
 
 template <typename T>
 __global__ void __launch_bounds__(kThreads, 1) decode_fused_kernel(const __grid_constant__ DecodeParams p) {
@@ -541,17 +567,13 @@ __global__ void __launch_bounds__(kThreads, 1) decode_fused_kernel(const __grid_
     // the pairs (0,4) (1,5) (2,6) (3,7) - the k order the unpacked weight words have.
     const int plane_bytes_x = d * 2, tok_stride = planes * plane_bytes_x + 64;
     uint8_t *xp = smem_raw + ((sizeof(Smem) + 127) & ~127);
-    float *xsum = reinterpret_cast<float *>(xp + M * tok_stride);  // [M][planes][d / 32]: plane sums over 32-code chunks
-    const int nchunk_x = d / 32;
-    uint8_t *stage_base = smem_raw + ((((uint8_t *)(xsum + M * planes * nchunk_x) - smem_raw) + 127) & ~127);
+    // plane sums of x over aligned runs of 32, 64 and 128 values: [M][planes][d/32 | d/64 | d/128] (a quantization group's sum is one load)
+    float *xsum = reinterpret_cast<float *>(xp + M * tok_stride);
+    const int nchunk_x = d / 32, xs_row = nchunk_x + nchunk_x / 2 + nchunk_x / 4;
+    uint8_t *stage_base = smem_raw + ((((uint8_t *)(xsum + M * planes * xs_row) - smem_raw) + 127) & ~127);
     float *xf = reinterpret_cast<float *>(stage_base);  // phases 0-1: x as FP32 [M][d], where the stages will be
 
     if (tid == 0) sm.abort_flag = 0, sm.failed_mask = 0, sm.n_groups = 0, sm.col_max = 1;
-    if (tid < kMaxStages) {
-        mbar_init(&sm.full_g[tid], 1), mbar_init(&sm.empty_g[tid], 1), mbar_init(&sm.full_d[tid], 1), mbar_init(&sm.empty_d[tid], 1);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        fence_proxy_async();
-    }
     stamp(p.sync, 0);
 
     // Phase 0: x -> FP32 copy, permuted planes, per-plane chunk sums.
@@ -598,9 +620,21 @@ __global__ void __launch_bounds__(kThreads, 1) decode_fused_kernel(const __grid_
         s_hi += __shfl_xor_sync(0xffffffffu, s_hi, 1), s_lo += __shfl_xor_sync(0xffffffffu, s_lo, 1);
         s_hi += __shfl_xor_sync(0xffffffffu, s_hi, 2), s_lo += __shfl_xor_sync(0xffffffffu, s_lo, 2);
         if (valid && (u & 3) == 0) {
-            xsum[(m * planes) * nchunk_x + u / 4] = s_hi;
-            if (planes == 2) xsum[(m * planes + 1) * nchunk_x + u / 4] = s_lo;
+            xsum[(m * planes) * xs_row + u / 4] = s_hi;
+            if (planes == 2) xsum[(m * planes + 1) * xs_row + u / 4] = s_lo;
         }
+    }
+    __syncthreads();
+    for (int i = tid; i < M * planes * (nchunk_x / 2); i += kThreads) {  // runs of 64
+        float *row = xsum + (i / (nchunk_x / 2)) * xs_row;
+        const int j = i % (nchunk_x / 2);
+        row[nchunk_x + j] = row[2 * j] + row[2 * j + 1];
+    }
+    __syncthreads();
+    for (int i = tid; i < M * planes * (nchunk_x / 4); i += kThreads) {  // runs of 128
+        float *row = xsum + (i / (nchunk_x / 4)) * xs_row;
+        const int j = i % (nchunk_x / 4);
+        row[nchunk_x + nchunk_x / 2 + j] = row[nchunk_x + 2 * j] + row[nchunk_x + 2 * j + 1];
     }
     __syncthreads();
     stamp(p.sync, 1);
@@ -652,68 +686,36 @@ __global__ void __launch_bounds__(kThreads, 1) decode_fused_kernel(const __grid_
         const int nk = p.gu_nk, Ks = d / nk;
         const int tiles_per_group = I / 8, n_tiles = NG * tiles_per_group;
         const int rs = p.gu_row_stride, sc_off = 16 * rs, sc_bytes = p.gu_scale_bytes, stage_bytes = p.gu_stage_bytes;
-        const Ring ring{p.gu_active, p.gu_depth};
+        const int D = p.gu_depth;  // stages per warp
         int n_local = 0;  // tiles of this CTA: blockIdx.x, blockIdx.x + gridDim.x, ..
         if ((int)blockIdx.x < n_tiles) n_local = (n_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1;
-
-        if (warp == 0) {
-            // producer: lanes 0..15 copy the row slices (low plane part, then high plane part), lanes 16..19 the scale runs
-            int gi = (int)blockIdx.x / tiles_per_group, jb = (int)blockIdx.x - gi * tiles_per_group;
-            int cw = 0, n = 0;  // the consumer warp and its stage count for the stage being issued
-            for (int tl = 0; tl < n_local; ++tl) {
-                const Group &grp = sm.groups[gi];
-                const int bits = grp.bits[0], gpr = d / grp.G[0];
-                const int rb = (int)row_bytes(bits, d), lo_b = slice_lo_bytes(bits, Ks), hi_b = slice_hi_bytes(bits, Ks);
-                const uint32_t tx = 16u * (lo_b + hi_b) + 4u * 8u * gpr * 2u;
-                const uint8_t *src = nullptr;
-                uint32_t src_bytes = 0;
-                if (lane < 16) {
-                    const int r = lane < 8 ? jb * 8 + lane : I + jb * 8 + (lane - 8);  // gate rows, then the matching up rows
-                    src = grp.rows[0] + (int64_t)r * rb;
-                } else if (lane < 20) {
-                    const int which = lane - 16;  // 0 gate scale, 1 gate min, 2 up scale, 3 up min
-                    const int r0 = (which & 2) ? I + jb * 8 : jb * 8;
-                    src = reinterpret_cast<const uint8_t *>(((which & 1) ? grp.minv[0] : grp.scale[0]) + (int64_t)r0 * gpr);
-                    src_bytes = 8u * gpr * 2u;
+        {
+            const int cw = warp, g = lane >> 2, c = lane & 3;
+            const int h = cw % nk, team = cw / nk, n_teams = CW / nk;
+            uint8_t *my_stages = stage_base + (size_t)cw * D * stage_bytes;
+            // the warp's n-th stage is slice h of tile team + n * n_teams; copies run D stages ahead of the math
+            auto issue = [&](int n) {
+                const int tl = team + n * n_teams;
+                if (tl < n_local) {
+                    const int t = (int)blockIdx.x + tl * (int)gridDim.x;
+                    const int gi = t / tiles_per_group;
+                    gu_issue(p, sm.groups[gi], t - gi * tiles_per_group, h, nk, my_stages + (size_t)(n % D) * stage_bytes, rs, sc_off, sc_bytes, lane);
                 }
-                bool ok = true;
-                for (int h = 0; h < nk; ++h) {
-                    const int slot = cw * ring.depth + n % ring.depth;
-                    const uint32_t ph = (uint32_t)(n / ring.depth) & 1u;
-                    if (lane == 0) ok = mbar_wait(&sm.empty_g[slot], ph ^ 1u, &sm.abort_flag, 1);
-                    ok = __shfl_sync(0xffffffffu, ok, 0);
-                    if (!ok) break;
-                    uint8_t *st = stage_base + (size_t)slot * stage_bytes;
-                    if (lane == 0) mbar_expect_tx(&sm.full_g[slot], tx);
-                    __syncwarp();
-                    if (lane < 16) {
-                        bulk_g2s(st + lane * rs, src + h * lo_b, lo_b, &sm.full_g[slot]);
-                        if (hi_b) bulk_g2s(st + lane * rs + lo_b, src + slice_lo_bytes(bits, d) + h * hi_b, hi_b, &sm.full_g[slot]);
-                    } else if (lane < 20) {
-                        bulk_g2s(st + sc_off + (lane - 16) * sc_bytes, src, src_bytes, &sm.full_g[slot]);
-                    }
-                    if (++cw == ring.active) cw = 0, ++n;
-                }
-                if (!ok) break;
-                jb += (int)gridDim.x;
-                while (jb >= tiles_per_group) jb -= tiles_per_group, ++gi;
-            }
-        } else if (warp - 1 < ring.active) {
-            const int cw = warp - 1, g = lane >> 2, c = lane & 3;
-            const int h = cw % nk, team = cw / nk, n_teams = ring.active / nk;
-            int n = 0;  // stages this warp has consumed
+                cp_async_commit();  // one group per stage, empty past the end: the wait below counts groups
+            };
+            for (int n = 0; n < D; ++n) issue(n);
+            int n = 0;
             for (int tl = team; tl < n_local; tl += n_teams, ++n) {
-                const int slot = cw * ring.depth + n % ring.depth;
-                const uint32_t ph = (uint32_t)(n / ring.depth) & 1u;
-                const bool ready = mbar_wait(&sm.full_g[slot], ph, &sm.abort_flag, 2);
+                cp_async_wait(D - 1);
+                __syncwarp();
                 const int t = (int)blockIdx.x + tl * (int)gridDim.x;
                 const int gi = t / tiles_per_group, jb = t - gi * tiles_per_group;
                 const Group &grp = sm.groups[gi];
                 const int np = (planes == 2 && (grp.mask >> 4)) ? 2 : 1;  // token passes
                 float tot[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-                if (ready) {
+                {
                     const int G = grp.G[0], gpr = d / G, gl = gpr / nk;  // groups per row, per slice
-                    const uint8_t *st = stage_base + (size_t)slot * stage_bytes;
+                    const uint8_t *st = my_stages + (size_t)(n % D) * stage_bytes;
                     const uint8_t *rowA = st + g * rs, *rowB = st + (g + 8) * rs;  // gate row g, up row g
                     const uint16_t *scA = reinterpret_cast<const uint16_t *>(st + sc_off) + g * gpr + h * gl;
                     const uint16_t *mnA = reinterpret_cast<const uint16_t *>(st + sc_off + sc_bytes) + g * gpr + h * gl;
@@ -730,36 +732,36 @@ __global__ void __launch_bounds__(kThreads, 1) decode_fused_kernel(const __grid_
 #pragma unroll
                         for (int e = 0; e < 2; ++e) {
                             column_of<planes>(2 * c + e, ps, tk, pl);
-                            if (ps < np && tk < M) xsp[ps][e] = xsum + (tk * planes + pl) * nchunk_x + h * (Ks / 32);
+                            if (ps < np && tk < M) xsp[ps][e] = xsum + (tk * planes + pl) * xs_row + (G == 32 ? 0 : G == 64 ? nchunk_x : nchunk_x + nchunk_x / 2) + h * gl;
                         }
                     }
                     by_bits(grp.bits[0], [&](auto bc) {
                         constexpr int BITS = decltype(bc)::value;
                         for (int qg = 0; qg < gl; ++qg) {
                             float xs[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
-                            for (int q = 0; q < G / 32; ++q) {
 #pragma unroll
-                                for (int ps = 0; ps < 2; ++ps)
+                            for (int ps = 0; ps < 2; ++ps)
 #pragma unroll
-                                    for (int e = 0; e < 2; ++e)
-                                        if (xsp[ps][e]) xs[ps][e] += xsp[ps][e][qg * (G / 32) + q];
-                            }
+                                for (int e = 0; e < 2; ++e)
+                                    if (xsp[ps][e]) xs[ps][e] = xsp[ps][e][qg];
                             const float sA = bf16_bits_to_f32(scA[qg]), mA = bf16_bits_to_f32(mnA[qg]), sB = bf16_bits_to_f32(scB[qg]), mB = bf16_bits_to_f32(mnB[qg]);
                             if (np == 1) {
                                 const uint8_t *const xb1[1] = {xb[0]};
                                 const float xs1[1][2] = {{xs[0][0], xs[0][1]}};
                                 float t1[1][4] = {{0.f, 0.f, 0.f, 0.f}};
-                                group_dot<BITS, 1>(rowA, rowB, Ks, xb1, qg * (G / 8), G / 32, c, sA, mA, sB, mB, xs1, t1);
+                                if (G == 128) group_dot<BITS, 1, 4>(rowA, rowB, Ks, xb1, qg * 16, 4, c, sA, mA, sB, mB, xs1, t1);
+                                else group_dot<BITS, 1, 0>(rowA, rowB, Ks, xb1, qg * (G / 8), G / 32, c, sA, mA, sB, mB, xs1, t1);
 #pragma unroll
                                 for (int i = 0; i < 4; ++i) tot[0][i] += t1[0][i];
                             } else {
                                 const uint8_t *const xb2[2] = {xb[0], xb[1]};
-                                group_dot<BITS, 2>(rowA, rowB, Ks, xb2, qg * (G / 8), G / 32, c, sA, mA, sB, mB, xs, tot);
+                                if (G == 128) group_dot<BITS, 2, 4>(rowA, rowB, Ks, xb2, qg * 16, 4, c, sA, mA, sB, mB, xs, tot);
+                                else group_dot<BITS, 2, 0>(rowA, rowB, Ks, xb2, qg * (G / 8), G / 32, c, sA, mA, sB, mB, xs, tot);
                             }
                         }
                     });
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&sm.empty_g[slot]);  // the stage refills while the tile is finished
+                    __syncwarp();      // every lane is done with the stage
+                    issue(n + D);      // refill it while the tile is finished
                 }
                 // the team's slices meet in its leader (h == 0): ordered sum, then the SwiGLU, lane-local
                 const int par = n & 1;
@@ -799,7 +801,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_fused_kernel(const __grid_
                             column_of<planes>(2 * c + e, ps, tok, pl);
                             const bool live = pl == 0 && tok < M && (grp.mask >> tok & 1u);
                             const float gs = as_stored(tot[ps][e], hh), us = as_stored(tot[ps][2 + e], hh);
-                            const float hv = as_stored(as_stored(silu_f(gs), hh) * us, hh);
+                            const float hv = as_stored(as_stored(__fdividef(gs, 1.0f + __expf(-gs)), hh) * us, hh);
                             const uint16_t hb = f32_to_bf16_bits(hv);
                             const uint16_t hl = planes == 2 ? f32_to_bf16_bits(hv - bf16_bits_to_f32(hb)) : (uint16_t)0;
                             part_hi[e] = live ? bf16_bits_to_f32(hb) : 0.f, part_lo[e] = live ? bf16_bits_to_f32(hl) : 0.f;
@@ -835,13 +837,11 @@ __global__ void __launch_bounds__(kThreads, 1) decode_fused_kernel(const __grid_
             }
         }
     }
+    cp_async_wait(0);
     stamp(p.sync, 5);
-    // h records are read by bulk copies (the async proxy) in other CTAs after the barrier
-    __threadfence();
-    fence_proxy_async();
+    // the h records written above are read by other CTAs after the barrier
     grid_arrive(&counters[1]);
     if (!grid_wait(&counters[1], &counters[3], sm)) goto abort;
-    fence_proxy_async();
     stamp(p.sync, 6);
 
     {
@@ -852,67 +852,46 @@ __global__ void __launch_bounds__(kThreads, 1) decode_fused_kernel(const __grid_
         const int rs = p.dn_row_stride, sc_off = 16 * rs, sc_bytes = p.dn_scale_bytes;
         const int col_off = p.dn_stage_bytes_fixed;
         const int stage_bytes = (col_off + sm.col_max * p.hrec_bytes + 127) & ~127;
-        int NS = avail3 / stage_bytes;
-        NS = NS > kMaxStages ? kMaxStages : NS;
-        if (NS < 1) {
+        // warps in use and stages per warp: all CW warps when a stage each fits, fewer (deeper is never needed then) otherwise
+        int ACT = avail3 / stage_bytes;
+        ACT = ACT > CW ? CW : ACT;
+        if (ACT < 1) {
             if (tid == 0) sm.abort_flag = 0x106;
             __syncthreads();
             goto abort;
         }
-        const Ring ring{NS >= CW ? CW : NS, NS >= CW ? NS / CW : 1};
+        int D = avail3 / (stage_bytes * ACT);
+        D = D > kMaxDepth ? kMaxDepth : D;
         const int n_blocks = d / 16;
         int nb_local = 0;
         if ((int)blockIdx.x < n_blocks) nb_local = (n_blocks - 1 - (int)blockIdx.x) / (int)gridDim.x + 1;
         const int part_off = planes * I * 2;  // the partial sums inside an h record
-        if (warp == 0) {
-            int cw = 0, n = 0;
-            bool ok = true;
-            for (int nbi = 0; nbi < nb_local && ok; ++nbi) {
-                const int nb = (int)blockIdx.x + nbi * (int)gridDim.x;
-                for (int gi = 0; gi < NG; ++gi) {
-                    const int slot = cw * ring.depth + n % ring.depth;
-                    const uint32_t ph = (uint32_t)(n / ring.depth) & 1u;
-                    if (lane == 0) ok = mbar_wait(&sm.empty_d[slot], ph ^ 1u, &sm.abort_flag, 3);
-                    ok = __shfl_sync(0xffffffffu, ok, 0);
-                    if (!ok) break;
-                    const Group &grp = sm.groups[gi];
-                    const int bits = grp.bits[1], gpr = I / grp.G[1];
-                    const int rb = (int)row_bytes(bits, I);
-                    const int ncol = __popc(grp.mask);
-                    const uint32_t run = (uint32_t)((16 * gpr * 2 + 15) & ~15);
-                    uint8_t *st = st3 + (size_t)slot * stage_bytes;
-                    if (lane == 0) mbar_expect_tx(&sm.full_d[slot], 16u * rb + 2u * run + (uint32_t)ncol * p.hrec_bytes);
-                    __syncwarp();
-                    if (lane < 16) {
-                        bulk_g2s(st + lane * rs, grp.rows[1] + ((int64_t)nb * 16 + lane) * rb, rb, &sm.full_d[slot]);
-                    } else if (lane < 18) {
-                        const uint16_t *src = (lane == 16 ? grp.scale[1] : grp.minv[1]) + (int64_t)nb * 16 * gpr;
-                        bulk_g2s(st + sc_off + (lane - 16) * sc_bytes, src, run, &sm.full_d[slot]);
-                    } else if (lane - 18 < ncol) {
-                        const int m = (int)__fns(grp.mask, 0, lane - 18 + 1);  // the (lane - 18)-th routed token's h record
-                        const int slot_i = grp.expert == -2 ? M * A + m : m * A + grp.slot_a[m];
-                        bulk_g2s(st + col_off + (lane - 18) * p.hrec_bytes, p.hrec + (int64_t)slot_i * p.hrec_bytes, p.hrec_bytes, &sm.full_d[slot]);
-                    }
-                    if (++cw == ring.active) cw = 0, ++n;
+        {
+            const int cw = warp, g = lane >> 2, c = lane & 3;
+            uint8_t *my_stages = st3 + (size_t)cw * D * stage_bytes;
+            // stages are numbered it = nbi * NG + gi over this CTA's row blocks; the warp takes it = cw, cw + ACT, ..
+            const int n_total = cw < ACT ? nb_local * NG : 0;
+            auto issue = [&](int n) {
+                const int it = cw + n * ACT;
+                if (it < n_total) {
+                    const int nbi = it / NG;
+                    dn_issue(p, sm.groups[it - nbi * NG], (int)blockIdx.x + nbi * (int)gridDim.x, my_stages + (size_t)(n % D) * stage_bytes, rs, sc_off,
+                             sc_bytes, col_off, lane);
                 }
-            }
-        } else {
-            const int cw = warp - 1, g = lane >> 2, c = lane & 3;
+                cp_async_commit();
+            };
+            for (int n = 0; n < D; ++n) issue(n);
             int n = 0;
             for (int nbi = 0; nbi < nb_local; ++nbi) {
                 const int nb = (int)blockIdx.x + nbi * (int)gridDim.x;
                 float tot[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}}, tot_sh[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-                // this warp's stages: it == cw (mod active) inside [nbi * NG, (nbi + 1) * NG)
-                int it = nbi * NG;
-                it += ((cw - it) % ring.active + ring.active) % ring.active;
-                if (cw >= ring.active) it = (nbi + 1) * NG;
-                for (; it < (nbi + 1) * NG; it += ring.active, ++n) {
-                    const int slot = cw * ring.depth + n % ring.depth;
-                    const uint32_t ph = (uint32_t)(n / ring.depth) & 1u;
-                    if (!mbar_wait(&sm.full_d[slot], ph, &sm.abort_flag, 4)) continue;  // gave up: keep walking so every warp meets below
+                for (int it = cw + n * ACT; cw < ACT && it < (nbi + 1) * NG; it += ACT, ++n) {
+                    cp_async_wait(D - 1);
+                    __syncwarp();
+                    const int slot = n % D;
                     const Group &grp = sm.groups[it - nbi * NG];
                     const int G = grp.G[1], gpr = I / G;
-                    const uint8_t *st = st3 + (size_t)slot * stage_bytes;
+                    const uint8_t *st = my_stages + (size_t)slot * stage_bytes;
                     const uint8_t *rowA = st + g * rs, *rowB = st + (g + 8) * rs;
                     const uint16_t *sc = reinterpret_cast<const uint16_t *>(st + sc_off), *mn = reinterpret_cast<const uint16_t *>(st + sc_off + sc_bytes);
                     const int np = (planes == 2 && (grp.mask >> 4)) ? 2 : 1;
@@ -939,13 +918,19 @@ __global__ void __launch_bounds__(kThreads, 1) decode_fused_kernel(const __grid_
                         constexpr int BITS = decltype(bc)::value;
                         for (int qg = 0; qg < gpr; ++qg) {
                             float xs[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
-                            for (int u = 0; u < G / 8; ++u) {
 #pragma unroll
-                                for (int ps = 0; ps < 2; ++ps)
+                            for (int ps = 0; ps < 2; ++ps)
 #pragma unroll
-                                    for (int e = 0; e < 2; ++e)
-                                        if (hp[ps][e]) xs[ps][e] += hp[ps][e][qg * (G / 8) + u];
-                            }
+                                for (int e = 0; e < 2; ++e)
+                                    if (hp[ps][e]) {
+                                        const float4 *v4 = reinterpret_cast<const float4 *>(hp[ps][e] + qg * (G / 8));
+                                        float a = 0.f;
+                                        for (int u = 0; u < G / 32; ++u) {
+                                            const float4 f = v4[u];
+                                            a += (f.x + f.y) + (f.z + f.w);
+                                        }
+                                        xs[ps][e] = a;
+                                    }
                             const float sA = bf16_bits_to_f32(sc[g * gpr + qg]), mA = bf16_bits_to_f32(mn[g * gpr + qg]);
                             const float sB = bf16_bits_to_f32(sc[(g + 8) * gpr + qg]), mB = bf16_bits_to_f32(mn[(g + 8) * gpr + qg]);
                             float v[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
@@ -953,12 +938,14 @@ __global__ void __launch_bounds__(kThreads, 1) decode_fused_kernel(const __grid_
                                 const uint8_t *const xb1[1] = {xb[0]};
                                 const float xs1[1][2] = {{xs[0][0], xs[0][1]}};
                                 float t1[1][4] = {{0.f, 0.f, 0.f, 0.f}};
-                                group_dot<BITS, 1>(rowA, rowB, I, xb1, qg * (G / 8), G / 32, c, sA, mA, sB, mB, xs1, t1);
+                                if (G == 128) group_dot<BITS, 1, 4>(rowA, rowB, I, xb1, qg * 16, 4, c, sA, mA, sB, mB, xs1, t1);
+                                else group_dot<BITS, 1, 0>(rowA, rowB, I, xb1, qg * (G / 8), G / 32, c, sA, mA, sB, mB, xs1, t1);
 #pragma unroll
                                 for (int i = 0; i < 4; ++i) v[0][i] = t1[0][i];
                             } else {
                                 const uint8_t *const xb2[2] = {xb[0], xb[1]};
-                                group_dot<BITS, 2>(rowA, rowB, I, xb2, qg * (G / 8), G / 32, c, sA, mA, sB, mB, xs, v);
+                                if (G == 128) group_dot<BITS, 2, 4>(rowA, rowB, I, xb2, qg * 16, 4, c, sA, mA, sB, mB, xs, v);
+                                else group_dot<BITS, 2, 0>(rowA, rowB, I, xb2, qg * (G / 8), G / 32, c, sA, mA, sB, mB, xs, v);
                             }
 #pragma unroll
                             for (int ps = 0; ps < 2; ++ps) {
@@ -972,7 +959,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_fused_kernel(const __grid_
                         }
                     });
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(&sm.empty_d[slot]);
+                    issue(n + D);
                     if (is_sh) {
                         float4 *dst = reinterpret_cast<float4 *>(&sm.red_sh[nbi & 1][lane][0]);
                         dst[0] = make_float4(tot_sh[0][0], tot_sh[0][1], tot_sh[0][2], tot_sh[0][3]);
@@ -986,7 +973,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_fused_kernel(const __grid_
                     dst[1] = make_float4(tot[1][0], tot[1][1], tot[1][2], tot[1][3]);
                 }
                 named_sync(1, CW * 32);
-                const int ct = tid - 32;
+                const int ct = tid;
                 if (ct < 128 && !sm.abort_flag) {
                     const int r = ct >> 3, tok = ct & 7;  // output row nb * 16 + r, token tok
                     if (tok < M) {
@@ -1014,6 +1001,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_fused_kernel(const __grid_
     }
 
     // The last CTA out zeroes the barrier words for the next launch.
+    cp_async_wait(0);
     __syncthreads();
     stamp(p.sync, 7);
     if (sm.abort_flag) goto abort;
@@ -1052,30 +1040,28 @@ int decode_fused_plan(DecodeParams &p, int max_bits_gate_up, int max_bits_down, 
     const int planes = p.act == kF32 ? 2 : 1;
     p.smem_bytes = max_smem;
     p.hrec_bytes = planes * (p.I * 2 + (p.I / 8) * 4);
-    const int fixed = (int)((sizeof(Smem) + 127) & ~127) + p.M * (planes * p.d * 2 + 64) + p.M * planes * (p.d / 32) * 4 + 256;
+    const int fixed = (int)((sizeof(Smem) + 127) & ~127) + p.M * (planes * p.d * 2 + 64) + p.M * planes * (p.d / 32 + p.d / 64 + p.d / 128) * 4 + 256;
     if (fixed + p.M * p.d * 4 > max_smem) return 0;  // the FP32 copy of x lives where the stages will be
-    // K slices per gate/up tile (1, 2 or 4: a divisor of the consumer warps): the fewest that give every consumer warp
-    // two stages of its own, else the most stages; slices stay multiples of 128 codes (16-byte pieces of both planes).
+    // K slices per gate/up tile (1, 2 or 4: a divisor of the warp count): the fewest that give every warp two stages of its
+    // own, else the deepest; slices stay multiples of 128 codes (16-byte pieces of both code planes).
     p.gu_scale_bytes = 8 * (p.d / min_G) * 2;
-    int best_nk = 0, best_stages = 0;
+    int best_nk = 0, best_depth = 0;
     for (int nk = 1; nk <= 4; nk *= 2) {
         const int Ks = p.d / nk;
         if (Ks % 128 != 0) break;
         const int stride = slice_lo_bytes(max_bits_gate_up, Ks) + slice_hi_bytes(max_bits_gate_up, Ks) + 16;
         const int stage = (16 * stride + 4 * p.gu_scale_bytes + 127) & ~127;
-        int stages = (max_smem - fixed) / stage;
-        if (stages > kMaxStages) stages = kMaxStages;
-        if (stages > best_stages) best_stages = stages, best_nk = nk;
-        if (stages >= 2 * CW) break;
+        int depth = (max_smem - fixed) / (stage * CW);
+        if (depth > kMaxDepth) depth = kMaxDepth;
+        if (depth > best_depth) best_depth = depth, best_nk = nk;
+        if (depth >= 2) break;
     }
-    if (best_nk == 0 || best_stages < best_nk) return 0;
+    if (best_nk == 0 || best_depth < 1) return 0;
     p.gu_nk = best_nk;
     const int Ks = p.d / best_nk;
     p.gu_row_stride = slice_lo_bytes(max_bits_gate_up, Ks) + slice_hi_bytes(max_bits_gate_up, Ks) + 16;
     p.gu_stage_bytes = (16 * p.gu_row_stride + 4 * p.gu_scale_bytes + 127) & ~127;
-    if (best_stages >= CW) p.gu_active = CW, p.gu_depth = best_stages / CW;
-    else p.gu_active = best_stages / best_nk * best_nk, p.gu_depth = 1;
-    p.gu_stages = p.gu_active * p.gu_depth;
+    p.gu_active = CW, p.gu_depth = best_depth, p.gu_stages = CW * best_depth;
     p.dn_row_stride = (int)row_bytes(max_bits_down, p.I) + 16;
     p.dn_scale_bytes = (16 * (p.I / min_G) * 2 + 15) & ~15;
     p.dn_stage_bytes_fixed = 16 * p.dn_row_stride + 2 * p.dn_scale_bytes;
