@@ -175,6 +175,9 @@ int strix_linear_q4_experts_combine_grouped(const void *h, const strix_qview *w,
 int strix_linear_q5_experts_combine_grouped(const void *h, const strix_qview *w, int64_t E, const int32_t *ids,
                                             const float *coef, const void *ws, size_t ws_bytes, float *partial,
                                             int64_t M, int64_t A, void *y, int act, int math, void *stream);
+/* Number of thread blocks of the tensor-core grouped GEMM that abandoned a bounded wait since the library was loaded:
+ * 0 in a healthy run (their outputs are undefined otherwise). No counterpart in the reference. Synchronizes. */
+unsigned int strix_umma_abort_count(void);
 /* The grouped pair over a stack with a format per expert. No counterpart in the reference. */
 int strix_linear_qmix_experts_gather_grouped(const void *x, const strix_qmix_view *w, const void *ws, size_t ws_bytes,
                                              int64_t M, int64_t A, void *y, int act, int math, void *stream);

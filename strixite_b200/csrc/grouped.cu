@@ -325,6 +325,8 @@ int mixed_view(const char *fn, const strix_qmix_view *w, StackView *out) {
 
 extern "C" {
 
+unsigned int strix_umma_abort_count(void) { return sb::grouped_umma_aborts(); }
+
 size_t strix_moe_route_workspace_bytes(int64_t M, int64_t A, int64_t E) {
     int64_t ints = 0;
     if (sb::route_ints(M, A, E, &ints) != 0) return 0;

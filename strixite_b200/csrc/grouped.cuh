@@ -27,4 +27,7 @@ __host__ __device__ inline RouteTables route_tables(const int32_t *ws, int64_t S
 int grouped_umma(const char *fn, const void *x, const StackView &w, const int32_t *ws, int64_t M, int64_t A, void *y,
                  float *partial, int act, bool combine, cudaStream_t stream);
 
+// CTAs of the tensor-core grouped GEMM that gave up on a bounded wait since the library was loaded (0 in a healthy run).
+unsigned int grouped_umma_aborts();
+
 }  // namespace sb

@@ -307,3 +307,61 @@ def test_grouped_bad_id():
     K.linear_q4_experts_gather_grouped(to_torch_act(x), upload_stack(gu_st), E, ws, nbytes, M, A, y, K.Act.F32, K.MoeMath.F32)
     yy = y.cpu().numpy()
     assert host_err(err) == [1, 99, 15] and np.all(np.isnan(yy[7, 1])) and np.isnan(yy).sum() == 2 * I
+
+
+@pytest.mark.parametrize("act", ACTS)
+@pytest.mark.parametrize("cfg", STACKS)
+@pytest.mark.parametrize("M,A", [(45, 4), (300, 3)])
+def test_experts_grouped_tensor_cores(act, cfg, M, A):
+    """The tcgen05 grouped GEMM (MoeMath WmmaBf16 / WmmaF16) against the oracle. Weights are rounded to BF16 on the way to
+    the tensor cores (and FP32 activations too): the contract is 2e-3 of the row maximum, FP32 accumulation."""
+    rng = np.random.default_rng(31 + M)
+    E, I, d = 9, 128, 256
+    gu_st = make_stack(rng, E, 2 * I, d, cfg["G"], cfg["bits"], cfg.get("mix"))
+    dn_st = make_stack(rng, E, d, I, cfg["G"], cfg["bits"], cfg.get("mix"))
+    x = randn_act(rng, (M, d), act)
+    ids = np.stack([rng.permutation(E)[:A] for _ in range(M)]).astype(np.int32)
+    ids[:, 0] = 2  # a hot expert: several 128-token tiles at M = 300
+    coef = rng.random((M, A)).astype(np.float32)
+    xt, idt, ct = to_torch_act(x), torch.from_numpy(ids).cuda(), torch.from_numpy(coef).cuda()
+    nbytes = K.moe_route_workspace_bytes(M, A, E)
+    ws = torch.empty(nbytes // 4, dtype=torch.int32, device="cuda")
+    err = dev_err()
+    K.moe_group_routes(idt, M, A, E, ws, nbytes, err)
+    tol = 2e-3 + (BF16_ULP if act == oracle.BF16 else 0.0)
+    for math in (K.MoeMath.WmmaBf16, K.MoeMath.WmmaF16):
+        y = torch.full((M, A, 2 * I), float("nan"), dtype=K._dtype(act), device="cuda")
+        K.linear_qw_experts_gather_grouped(xt, K.qweight(upload_stack(gu_st)), E, ws, nbytes, M, A, y, act, math)
+        ref, _ = oracle.experts_gather(x, gu_st, ids)
+        assert rel_err_rows(oracle.to_f32(to_np_act(y)), oracle.to_f32(ref)) < tol
+        href, _ = oracle.experts_gather(x, gu_st, ids, swiglu=True)
+        yref, _ = oracle.experts_combine(href, dn_st, ids, coef)
+        partial = torch.empty((M * A * d,), dtype=torch.float32, device="cuda")
+        yc = torch.full((M, d), float("nan"), dtype=K._dtype(act), device="cuda")
+        K.linear_qw_experts_combine_grouped(to_torch_act(href), K.qweight(upload_stack(dn_st)), E, idt, ct, ws, nbytes, partial, M, A, yc, act, math)
+        assert rel_err_rows(oracle.to_f32(to_np_act(yc)), oracle.to_f32(yref)) < tol
+    from strixite_b200._lib import lib
+
+    assert lib.strix_umma_abort_count() == 0
+
+
+def test_grouped_tensor_cores_bad_id_and_k_check():
+    rng = np.random.default_rng(23)
+    E, I, d, M, A = 5, 64, 128, 20, 2
+    gu_st = make_stack(rng, E, 2 * I, d, 32)
+    x = randn_act(rng, (M, d), oracle.BF16)
+    ids = np.stack([rng.permutation(E)[:A] for _ in range(M)]).astype(np.int32)
+    ids[7, 1] = 99
+    nbytes = K.moe_route_workspace_bytes(M, A, E)
+    ws = torch.empty(nbytes // 4, dtype=torch.int32, device="cuda")
+    err = dev_err()
+    K.moe_group_routes(torch.from_numpy(ids).cuda(), M, A, E, ws, nbytes, err)
+    y = torch.zeros((M, A, 2 * I), dtype=torch.bfloat16, device="cuda")
+    K.linear_q4_experts_gather_grouped(to_torch_act(x), upload_stack(gu_st), E, ws, nbytes, M, A, y, K.Act.BF16, K.MoeMath.WmmaBf16)
+    yy = y.float().cpu().numpy()
+    assert host_err(err) == [1, 99, 15] and np.all(np.isnan(yy[7, 1])) and np.isnan(yy).sum() == 2 * I
+    # K must be a multiple of 64 on the tensor path (strixite kernels/moe_grouped.hip:515,528)
+    st32 = make_stack(rng, E, 64, 96, 32)
+    with pytest.raises(StrixError, match="multiple of 64"):
+        K.linear_q4_experts_gather_grouped(torch.zeros((M, 96), dtype=torch.bfloat16, device="cuda"), upload_stack(st32), E, ws, nbytes, M, A,
+                                           torch.zeros((M, A, 64), dtype=torch.bfloat16, device="cuda"), K.Act.BF16, K.MoeMath.WmmaBf16)
