@@ -27,8 +27,10 @@ extern "C" {
 #define STRIX_ACT_BF16 1
 
 /* strixite kernels/moe_grouped.hpp:30-35 enum class MoeMath. F32: FP32 FMA on the CUDA cores. WMMA_BF16 / WMMA_F16:
- * both select the tensor-core path here (activations BF16, weights dequantized to BF16 in shared memory, FP32
- * accumulation in tensor memory, FP32 combine partials). */
+ * both select the tensor-core path here: activations and dequantized weights as F16 operands in shared memory (one
+ * F16 rounding of code * s + m, the precision of the reference's WmmaF16; BF16 activations convert exactly inside
+ * F16's normal range, |x| < 65504, the assumption of strixite kernels/wmma_gemm.hpp:371-372), FP32 accumulation in
+ * tensor memory, FP32 combine partials. */
 #define STRIX_MATH_F32 0
 #define STRIX_MATH_WMMA_BF16 1
 #define STRIX_MATH_WMMA_F16 2
