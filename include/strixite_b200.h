@@ -177,6 +177,22 @@ int strix_linear_q4_experts_combine_grouped(const void *h, const strix_qview *w,
 int strix_linear_q5_experts_combine_grouped(const void *h, const strix_qview *w, int64_t E, const int32_t *ids,
                                             const float *coef, const void *ws, size_t ws_bytes, float *partial,
                                             int64_t M, int64_t A, void *y, int act, int math, void *stream);
+/* linear_q4_experts_combine_grouped without the `partial` argument: the M * A * N partial sums go to a fixed array of
+ * STRIX_FIXED_PARTIAL_FLOATS floats (4 MiB) that is part of the library's device image. No counterpart in the
+ * reference. It is for callers that have no buffer to give and may not allocate one at the call site: a host that has
+ * handed all device memory to its own pool, or a latency-critical loop in which cudaMalloc (which can synchronize the
+ * whole device) is ruled out. The call itself allocates nothing, on the host or the device.
+ *   - Limit: M * A * N <= STRIX_FIXED_PARTIAL_FLOATS, else the call fails (1) before anything is enqueued; larger
+ *     shapes use the variant above with a caller-provided buffer.
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that device
+ *     current) and caches it; make that first call outside any stream capture.
+ *   - Every call on a device uses the same array. Nothing in it has to be zero beforehand (each partial sum that is
+ *     read is written first by the same call), but two calls whose kernels can overlap in time - different streams,
+ *     or different host threads without ordering - race on it; calls on one stream are safe. */
+#define STRIX_FIXED_PARTIAL_FLOATS (1 << 20)
+int strix_linear_q4_experts_combine_grouped_fixed(const void *h, const strix_qview *w, int64_t E, const int32_t *ids,
+                                                  const float *coef, const void *ws, size_t ws_bytes, int64_t M,
+                                                  int64_t A, void *y, int act, int math, void *stream);
 /* Number of thread blocks of the tensor-core grouped GEMM that abandoned a bounded wait since the library was loaded:
  * 0 in a healthy run (their outputs are undefined otherwise). No counterpart in the reference. Synchronizes. */
 unsigned int strix_umma_abort_count(void);

@@ -8,6 +8,7 @@
 //   slots[S]         slot numbers (m * A + a) ordered by bucket, ascending inside a bucket
 //   tile_bucket[Tmax], tile_start[Tmax]      tiles of up to 16 slots of one bucket;  Tmax  = S / 16 + E + 2
 //   wtile_bucket[WTmax], wtile_start[WTmax]  tiles of up to 64 slots of one bucket;  WTmax = S / 64 + E + 2
+#include <mutex>
 #include "common.cuh"
 
 #include "grouped.cuh"
@@ -387,6 +388,46 @@ int strix_linear_q5_experts_combine_grouped(const void *h, const strix_qview *w,
     return sb::combine_grouped("linear_q5_experts_combine_grouped", h, sv, E, ids, coef, ws, ws_bytes, partial, M, A, y, act, math,
                                stream);
 }
+// ---- the combine with its partial sums in the library's own fixed device array -------------------------------------
+// The array lives in the library's device image, so it exists on every device the library runs on without any
+// allocation. Its name is a host-side handle, not a device address: the address comes from cudaGetSymbolAddress, asked
+// once per device with that device current, and cached.
+static __device__ __align__(256) float g_fixed_partial[STRIX_FIXED_PARTIAL_FLOATS];
+
+namespace {
+int fixed_partial(const char *fn, float **out) {
+    constexpr int kMaxDevices = 64;
+    static std::mutex mu;
+    static float *addr[kMaxDevices] = {};
+    int dev = -1;
+    SB_CUDA(cudaGetDevice(&dev), fn);
+    SB_CHECK(dev >= 0 && dev < kMaxDevices, fn, ": device ordinal ", dev, " outside 0..", kMaxDevices - 1);
+    std::lock_guard<std::mutex> lock(mu);
+    if (addr[dev] == nullptr) {
+        float *p = nullptr;
+        SB_CUDA(cudaGetSymbolAddress(reinterpret_cast<void **>(&p), g_fixed_partial), fn);
+        SB_CHECK(p != nullptr, fn, ": the fixed scratch array has no address on device ", dev);
+        addr[dev] = p;
+    }
+    *out = addr[dev];
+    return 0;
+}
+}  // namespace
+
+int strix_linear_q4_experts_combine_grouped_fixed(const void *h, const strix_qview *w, int64_t E, const int32_t *ids,
+                                                  const float *coef, const void *ws, size_t ws_bytes, int64_t M, int64_t A,
+                                                  void *y, int act, int math, void *stream) {
+    const char *fn = "linear_q4_experts_combine_grouped_fixed";
+    StackView sv;
+    SB_TRY(uniform_view(fn, 4, w, E, &sv));
+    SB_CHECK(M >= 1 && A >= 1 && sv.N >= 1 && M * A <= STRIX_FIXED_PARTIAL_FLOATS && M * A * sv.N <= STRIX_FIXED_PARTIAL_FLOATS, fn,
+             ": M * A * N = ", M, " * ", A, " * ", sv.N, " partial sums exceed the fixed scratch array of ", (int64_t)STRIX_FIXED_PARTIAL_FLOATS,
+             " floats; use linear_q4_experts_combine_grouped with a caller-provided buffer");
+    float *partial = nullptr;
+    SB_TRY(fixed_partial(fn, &partial));
+    return sb::combine_grouped(fn, h, sv, E, ids, coef, ws, ws_bytes, partial, M, A, y, act, math, stream);
+}
+
 int strix_linear_qmix_experts_gather_grouped(const void *x, const strix_qmix_view *w, const void *ws, size_t ws_bytes,
                                              int64_t M, int64_t A, void *y, int act, int math, void *stream) {
     StackView sv;

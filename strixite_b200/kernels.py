@@ -415,6 +415,17 @@ def linear_q4_experts_combine_grouped(h, w, E, ids, coef, ws, ws_bytes, partial,
     _combine_grouped(4, h, w, E, ids, coef, ws, ws_bytes, partial, M, A, y, act, math, stream)
 
 
+FIXED_PARTIAL_FLOATS = 1 << 20  # STRIX_FIXED_PARTIAL_FLOATS
+
+
+def linear_q4_experts_combine_grouped_fixed(h, w, E, ids, coef, ws, ws_bytes, M, A, y, act, math, stream=None):
+    """linear_q4_experts_combine_grouped with the partial sums in the library's fixed 4 MiB device array: no buffer to
+    pass, nothing allocated; M * A * N <= FIXED_PARTIAL_FLOATS; calls that may overlap in time race on the array."""
+    v = w.view() if isinstance(w, QWeight) else w
+    call("strix_linear_q4_experts_combine_grouped_fixed", _p(h), C.byref(v), E, _p(ids), _p(coef), _p(ws), ws_bytes, M, A, _p(y), int(act),
+         int(math), _s(stream))
+
+
 def linear_q5_experts_combine_grouped(h, w, E, ids, coef, ws, ws_bytes, partial, M, A, y, act, math, stream=None):
     """strixite kernels/moe_grouped.hpp:68-70."""
     _combine_grouped(5, h, w, E, ids, coef, ws, ws_bytes, partial, M, A, y, act, math, stream)
