@@ -49,28 +49,71 @@ def peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons during the timed region."""
+    """SM clock and throttle reasons during the timed region: NVML polled from a thread every ~5 ms (read-only queries),
+    nvidia-smi -lms as the fallback."""
 
     Q = "index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown," \
         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
 
     def __init__(self, index):
-        self.index, self.rows, self.proc = index, [], None
+        self.index, self.rows, self.proc, self.nv, self.stop_flag = index, [], None, None, False
+        self.sm, self.mx, self.reason_bits = [], None, 0
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q, "--format=csv,noheader,nounits", "-lms", "100"],
+            import pynvml as nv
+
+            nv.nvmlInit()
+            # CUDA_VISIBLE_DEVICES may renumber devices: find the NVML handle by the CUDA device's PCI bus id
+            import torch
+
+            bus = torch.cuda.get_device_properties(self.index).pci_bus_id if hasattr(torch.cuda.get_device_properties(self.index), "pci_bus_id") else None
+            self.h = None
+            if bus is not None:
+                for i in range(nv.nvmlDeviceGetCount()):
+                    h = nv.nvmlDeviceGetHandleByIndex(i)
+                    if nv.nvmlDeviceGetPciInfo(h).bus == bus:
+                        self.h = h
+            if self.h is None:
+                self.h = nv.nvmlDeviceGetHandleByIndex(self.index)
+            self.mx = float(nv.nvmlDeviceGetMaxClockInfo(self.h, nv.NVML_CLOCK_SM))
+            self.nv = nv
+            self.t = threading.Thread(target=self._poll, daemon=True)
+            self.t.start()
+            return
+        except Exception:  # noqa: BLE001  (no NVML binding: fall back to the command-line tool)
+            self.nv = None
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q, "--format=csv,noheader,nounits", "-lms", "20"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.t = threading.Thread(target=self._read, daemon=True)
             self.t.start()
         except OSError:
             self.proc = None
 
+    def _poll(self):
+        nv = self.nv
+        while not self.stop_flag:
+            try:
+                self.sm.append(float(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)))
+                self.reason_bits |= int(nv.nvmlDeviceGetCurrentClocksEventReasons(self.h))
+            except Exception:  # noqa: BLE001
+                pass
+            time.sleep(0.005)
+
     def _read(self):
         for line in self.proc.stdout:
             self.rows.append([c.strip() for c in line.split(",")])
 
     def stop(self):
+        if self.nv is not None:
+            self.stop_flag = True
+            self.t.join(timeout=2)
+            nv = self.nv
+            names = {"hw_slowdown": nv.nvmlClocksEventReasonHwSlowdown, "hw_thermal_slowdown": nv.nvmlClocksEventReasonHwThermalSlowdown,
+                     "sw_thermal_slowdown": nv.nvmlClocksEventReasonSwThermalSlowdown, "sw_power_cap": nv.nvmlClocksEventReasonSwPowerCap}
+            reasons = sorted(n for n, bit in names.items() if self.reason_bits & int(bit))
+            return dict(sm_mhz=float(np.median(self.sm)) if self.sm else None, sm_max_mhz=self.mx, reasons=reasons, samples=len(self.sm), source="nvml")
         if self.proc is None:
             return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
         self.proc.terminate()
@@ -82,7 +125,24 @@ class ClockSampler:
         mx = [float(r[2]) for r in self.rows if len(r) >= 9 and r[2].replace(".", "").isdigit()]
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         reasons = sorted({n for r in self.rows if len(r) >= 9 for n, v in zip(names, r[5:9]) if v.lower().startswith("active")})
-        return dict(sm_mhz=float(np.median(sm)) if sm else None, sm_max_mhz=max(mx) if mx else None, reasons=reasons, samples=len(sm))
+        return dict(sm_mhz=float(np.median(sm)) if sm else None, sm_max_mhz=max(mx) if mx else None, reasons=reasons, samples=len(sm), source="nvidia-smi")
+
+
+def kernel_nodes(graph):
+    """Kernel nodes of a captured step = kernels launched per replay."""
+    try:
+        from cuda.bindings import runtime as rt
+
+        raw = graph.raw_cuda_graph()
+        err, _, n = rt.cudaGraphGetNodes(raw, 0)
+        err, nodes, n = rt.cudaGraphGetNodes(raw, n)
+        k = 0
+        for nd in nodes[:n]:
+            err, ty = rt.cudaGraphNodeGetType(nd)
+            k += int(ty == rt.cudaGraphNodeType.cudaGraphNodeTypeKernel)
+        return k
+    except Exception:  # noqa: BLE001
+        return None
 
 
 def bytes_of_weight(N, Kdim, bits, G):
@@ -153,9 +213,10 @@ def capture(ring):
 
     graphs = []
     for e in ring:
-        g = torch.cuda.CUDAGraph()
+        g = torch.cuda.CUDAGraph(keep_graph=True)
         with torch.cuda.graph(g):
             step(e)
+        g.instantiate()
         graphs.append(g)
     return graphs
 
@@ -254,8 +315,8 @@ def cpu_baseline(ring, cfg, budget_s=12.0, max_tokens=None):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=400)
-    ap.add_argument("--warmup", type=int, default=40)
+    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--warmup", type=int, default=50)
     ap.add_argument("--workload", default="verify6", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -372,8 +433,11 @@ def main():
             ach = fl / step_s / 1e12
             line["roofline"] = dict(bound="tensor", achieved=ach, peak=P["tensor"], unit="TFLOP/s", frac=ach / P["tensor"], traffic=None,
                                     peak_source=P["source"], algorithmic_flops_per_step=fl, kernel="whole step")
-        launches = {"decode1": 4, "verify6": 11, "prefill4096": 7, "stack4": 4 * 5 + 1}[args.workload]
-        line["gpu_launches"] = launches * args.steps
+        per_step = [kernel_nodes(g) for g in graphs]
+        if any(k is None for k in per_step):
+            raise RuntimeError("could not count the kernel nodes of the captured steps")
+        line["gpu_launches"] = int(sum(per_step[(args.warmup + i) % n] for i in range(args.steps)))
+        line["gpu_launches_per_step"] = float(np.mean(per_step))
         if not args.no_cpu_baseline:
             line["cpu_baseline"], _ = cpu_baseline(ring, cfg, max_tokens=256 if cfg["M"] > 256 else None)
         print(json.dumps(line))

@@ -12,6 +12,7 @@
 #include "common.cuh"
 
 #include "grouped.cuh"
+#include "prefill_umma.cuh"
 #include "strixite_b200.h"
 
 namespace {
@@ -305,6 +306,15 @@ int combine_grouped(const char *fn, const void *h, const StackView &w, int64_t E
     return 0;
 }
 
+int combine_reduce(const char *fn, const float *partial, const int32_t *ids, const float *coef, int64_t M, int64_t A, int64_t E, int64_t N,
+                   void *y, int act, cudaStream_t st) {
+    const unsigned blocks = (unsigned)((M * N + 255) / 256);
+    if (act == kF32) combine_reduce_kernel<float><<<blocks, 256, 0, st>>>(partial, ids, coef, M, A, E, N, (float *)y);
+    else combine_reduce_kernel<uint16_t><<<blocks, 256, 0, st>>>(partial, ids, coef, M, A, E, N, (uint16_t *)y);
+    SB_LAUNCH_OK(fn, " reduce ", act_name(act), " M=", M, " A=", A, " N=", N);
+    return 0;
+}
+
 }  // namespace sb
 
 namespace {
@@ -326,7 +336,7 @@ int mixed_view(const char *fn, const strix_qmix_view *w, StackView *out) {
 
 extern "C" {
 
-unsigned int strix_umma_abort_count(void) { return sb::grouped_umma_aborts(); }
+unsigned int strix_umma_abort_count(void) { return sb::grouped_umma_aborts() + sb::prefill_aborts(); }
 
 size_t strix_moe_route_workspace_bytes(int64_t M, int64_t A, int64_t E) {
     int64_t ints = 0;

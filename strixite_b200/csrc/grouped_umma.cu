@@ -23,162 +23,20 @@
 // Every mbarrier wait is bounded; on expiry the CTA raises a global abort word (strix_umma_abort_count), frees its
 // tensor memory and returns.
 #include "grouped.cuh"
+#include "umma.cuh"
 
 namespace {
 
 using namespace sb;
+using namespace sb::umma;
 
 constexpr int kStages = 3;
 constexpr int kBK = 64;                   // K per stage: 64 F16 = one 128-byte swizzle row
-constexpr int kTileM = 128;               // weight rows per CTA (MMA M)
 constexpr int kTileN = 128;               // token rows per CTA at most (MMA N)
 constexpr int kStageBytesA = kTileM * kBK * 2, kStageBytesB = kTileN * kBK * 2;
 constexpr int kThreads = 160;
-constexpr uint32_t kSpinLimit = 1u << 22;
 
 __device__ unsigned int g_umma_aborts = 0;
-
-__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag) {
-    for (uint32_t i = 0; i < kSpinLimit; ++i) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 255u) == 0u && *abort_flag) return false;
-    }
-    *abort_flag = 1;
-    return false;
-}
-
-// K-major operand tile with 128-byte swizzle: rows of 128 bytes, 8-row groups of 1024 bytes; SBO = 1024 >> 4, LBO unused
-// (1), descriptor version 1, layout type 2 (SWIZZLE_128B). The tile base is 1024-byte aligned.
-__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
-    return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
-}
-// kind::f16 instruction descriptor: D = F32 (bits 4-5 = 1), A = B = F16 (format 0), both K-major, M = 128, N = n.
-__device__ __forceinline__ uint32_t umma_idesc(int n) {
-    return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
-}
-__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
-        ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u)
-        : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint64_t *bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-// (a & mask) | orv
-__device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t mask, uint32_t orv) {
-    uint32_t r;
-    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(a), "r"(mask), "r"(orv));
-    return r;
-}
-__device__ __forceinline__ uint32_t h2_sub(uint32_t a, uint32_t b) {
-    uint32_t r;
-    asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
-    return r;
-}
-__device__ __forceinline__ uint32_t h2_fma(uint32_t a, uint32_t b, uint32_t c) {
-    uint32_t r;
-    asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
-    return r;
-}
-__device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
-    uint32_t r;
-    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
-    return r;
-}
-// A BF16 value (scale or minimum) twice, as F16 pairs.
-__device__ __forceinline__ uint32_t bf16_to_h2(uint32_t b) {
-    const float f = __uint_as_float(b << 16);
-    return pack_h2(f, f);
-}
-
-// One 16-byte chunk (8 K elements in the order 0,4,1,5,2,6,3,7) of row r goes to chunk (j ^ (r & 7)) of the row.
-__device__ __forceinline__ void st_chunk(uint8_t *tile, int r, int j, uint4 v) {
-    *reinterpret_cast<uint4 *>(tile + (r >> 3) * 1024 + (r & 7) * 128 + ((j ^ (r & 7)) << 4)) = v;
-}
-
-// The 8 codes of one unit (codes 8u .. 8u + 7 of a row) as F16 pairs (0,4) (1,5) (2,6) (3,7) of code * s + m: one F16
-// rounding of the exact value (the precision of the reference's served path, strixite kernels/wmma_gemm.hpp:121-128).
-template <int BITS>
-__device__ __forceinline__ uint4 dequant_unit(const uint8_t *row, int64_t K, int u, uint32_t s2, uint32_t m2) {
-    uint32_t pr[4];
-    if constexpr (BITS == 4) {
-        const uint32_t w = __ldg(reinterpret_cast<const uint32_t *>(row) + u);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) pr[j] = lop3_and_or(w >> (4 * j), 0x000F000Fu, 0x64006400u);  // F16 1024 + code
-    } else {
-        // codes up to 255: through FP32 (exact in F16 too), then the same F16 FMA
-        int code[8];
-        if constexpr (BITS == 8) {
-            const uint2 w = __ldg(reinterpret_cast<const uint2 *>(row) + u);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) code[i] = ((i < 4 ? w.x : w.y) >> (8 * (i & 3))) & 0xFF;
-        } else {
-            const uint32_t w = __ldg(reinterpret_cast<const uint32_t *>(row) + u);
-            uint32_t hb;
-            if constexpr (BITS == 5) hb = row[K / 2 + u];
-            else hb = *reinterpret_cast<const uint16_t *>(row + K / 2 + 2 * u);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const int hi = BITS == 5 ? ((hb >> i) & 1) : ((hb >> (2 * i)) & 3);
-                code[i] = ((w >> (4 * i)) & 0xF) | (hi << 4);
-            }
-        }
-#pragma unroll
-        for (int j = 0; j < 4; ++j) pr[j] = pack_h2((float)code[j], (float)code[j + 4]);
-        uint4 o;
-        o.x = h2_fma(pr[0], s2, m2), o.y = h2_fma(pr[1], s2, m2), o.z = h2_fma(pr[2], s2, m2), o.w = h2_fma(pr[3], s2, m2);
-        return o;
-    }
-    uint4 o;
-    o.x = h2_fma(h2_sub(pr[0], 0x64006400u), s2, m2);
-    o.y = h2_fma(h2_sub(pr[1], 0x64006400u), s2, m2);
-    o.z = h2_fma(h2_sub(pr[2], 0x64006400u), s2, m2);
-    o.w = h2_fma(h2_sub(pr[3], 0x64006400u), s2, m2);
-    return o;
-}
-
-// 8 consecutive activations -> F16 pairs in the order (0,4) (1,5) (2,6) (3,7). BF16 inputs convert exactly inside F16's
-// normal range (the reference's served path makes the same assumption, strixite kernels/wmma_gemm.hpp:371-372).
-__device__ __forceinline__ uint4 act_chunk(const uint16_t *p) {
-    const uint4 v = __ldg(reinterpret_cast<const uint4 *>(p));  // (0,1) (2,3) (4,5) (6,7)
-    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-    float f[8];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) f[2 * i] = __uint_as_float(w[i] << 16), f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
-    uint4 o;
-    o.x = pack_h2(f[0], f[4]), o.y = pack_h2(f[1], f[5]), o.z = pack_h2(f[2], f[6]), o.w = pack_h2(f[3], f[7]);
-    return o;
-}
-__device__ __forceinline__ uint4 act_chunk(const float *p) {
-    const float4 a = __ldg(reinterpret_cast<const float4 *>(p)), b = __ldg(reinterpret_cast<const float4 *>(p) + 1);
-    uint4 o;
-    o.x = pack_h2(a.x, b.x), o.y = pack_h2(a.y, b.y), o.z = pack_h2(a.z, b.z), o.w = pack_h2(a.w, b.w);
-    return o;
-}
 
 struct Shared {
     uint64_t full[kStages], empty[kStages], acc_full;

@@ -4,6 +4,7 @@
 #include "common.cuh"
 
 #include "decode_fused.cuh"
+#include "prefill_umma.cuh"
 #include "strixite_b200.h"
 
 #include <cstring>
@@ -71,9 +72,13 @@ struct strix_moe_layer {
     uint32_t *sync = nullptr;
     bool fused_ok = false;
     sb::DecodeParams plan{};
+    // the tensor-core path for many tokens (math != F32, uniform 4-bit stacks)
+    sb::PrefillPlan *prefill = nullptr;
 };
 
 namespace {
+
+constexpr int64_t kPrefillMinTokens = 64;  // below this the FP32 grouped kernels do less padded work
 
 int check_desc(const strix_moe_layer_desc &d) {
     const char *fn = "moe_layer_create";
@@ -182,6 +187,8 @@ int strix_moe_layer_create(const strix_moe_layer_desc *desc, strix_moe_layer **o
             if (rc == 0 && cudaMemset(L->sync, 0, 512) != cudaSuccess) rc = STRIX_ERR_CUDA;
         }
     }
+    if (rc == 0 && d.math != STRIX_MATH_F32 && sb::prefill_supported(d) && T >= kPrefillMinTokens)
+        rc = sb::prefill_create(d, L->A, L->Estack, L->router_rows, &L->prefill);
     if (rc == 0 && cudaMemset(L->err, 0, 32) != cudaSuccess) rc = STRIX_ERR_CUDA;
     if (rc == 0 && cudaMallocHost(&L->pin_x, (size_t)(T * d.d * es)) != cudaSuccess) rc = STRIX_ERR_CUDA;
     if (rc == 0 && cudaMallocHost(&L->pin_y, (size_t)(T * d.d * es)) != cudaSuccess) rc = STRIX_ERR_CUDA;
@@ -200,6 +207,7 @@ void strix_moe_layer_destroy(strix_moe_layer *L) {
     void *dev[] = {L->logits, L->ids, L->coef, L->ids_k, L->coef_k, L->gu, L->hh, L->sh_h, L->sh_y, L->partial, L->group_ws, L->err, L->dev_x, L->dev_y, L->hrec, L->sync};
     for (void *p : dev)
         if (p) cudaFree(p);
+    sb::prefill_destroy(L->prefill);
     if (L->pin_x) cudaFreeHost(L->pin_x);
     if (L->pin_y) cudaFreeHost(L->pin_y);
     if (L->pin_err) cudaFreeHost(L->pin_err);
@@ -243,7 +251,9 @@ int strix_moe_layer_forward(strix_moe_layer *L, const void *x, int64_t M, void *
         return 0;
     }
     // 1. Router logits, FP32 [M, R]; row E (when gated) is the shared expert's gate.
-    if (d.router_kind == STRIX_ROUTER_Q) SB_TRY(linear_any(d.router_bits, x, &d.router_q, L->logits, M, act, STRIX_ACT_F32, stream));
+    const bool tensor_path = L->prefill != nullptr && M >= kPrefillMinTokens;
+    if (tensor_path && sb::prefill_has_dense_router(L->prefill)) SB_TRY(sb::prefill_router_logits(L->prefill, x, M, L->logits, st));
+    else if (d.router_kind == STRIX_ROUTER_Q) SB_TRY(linear_any(d.router_bits, x, &d.router_q, L->logits, M, act, STRIX_ACT_F32, stream));
     else if (d.router_kind == STRIX_ROUTER_BF16)
         SB_TRY(strix_linear_bf16w(x, static_cast<const uint16_t *>(d.router_w), L->logits, M, R, d.d, act, STRIX_ACT_F32, stream));
     else SB_TRY(strix_linear_f32w(x, static_cast<const float *>(d.router_w), L->logits, M, R, d.d, act, STRIX_ACT_F32, stream));
@@ -264,7 +274,13 @@ int strix_moe_layer_forward(strix_moe_layer *L, const void *x, int64_t M, void *
                                 router_err, stream));
     }
     // 3. Routed experts: grouped from grouped_min_tokens on, per slot below.
-    if (M >= d.grouped_min_tokens) {
+    if (tensor_path) {
+        // many tokens on the tensor cores: bucket-ordered F16 activations, gate/up with SwiGLU in its epilogue, down into
+        // FP32 partials, then the ordered reduction of the reference's combine
+        SB_TRY(strix_moe_group_routes(L->ids, M, A, L->Estack, L->group_ws, L->group_ws_bytes, expert_err, stream));
+        SB_TRY(sb::prefill_experts(L->prefill, x, act, static_cast<const int32_t *>(L->group_ws), M, L->partial, st));
+        SB_TRY(sb::combine_reduce(fn, L->partial, L->ids, L->coef, M, A, L->Estack, d.d, y, act, st));
+    } else if (M >= d.grouped_min_tokens) {
         SB_TRY(strix_moe_group_routes(L->ids, M, A, L->Estack, L->group_ws, L->group_ws_bytes, expert_err, stream));
         if (d.experts_mixed) {
             SB_TRY(strix_linear_qmix_experts_gather_grouped(x, &d.gate_up_mix, L->group_ws, L->group_ws_bytes, M, A, L->gu, act, d.math, stream));

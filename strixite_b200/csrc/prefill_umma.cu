@@ -1,0 +1,553 @@
+// The many-token expert FFN on the 5th-generation tensor cores: persistent, warp-specialised tcgen05 kernels fed by TMA.
+//
+//   dense_umma_kernel   router logits[M, R] = x[M, d] * Wr[R, d]^T for BF16 activations and a BF16 router (products of
+//                       two BF16 values are exact in FP32, so this equals the FP32-FMA projection up to summation
+//                       order). Both operands arrive by TMA with the 128-byte swizzle; no thread touches them.
+//   tiles_kernel        the per-expert buckets of the grouping workspace cut into tiles of at most 128 routed slots.
+//   pregather_kernel    xg[p, :] = F16(x[token of sorted slot p, :]): the activations in bucket order, so that a tile's
+//                       tokens are 128 consecutive rows one TMA box can fetch.
+//   ffn_umma_kernel<0>  hs[p, i] = SwiGLU(gate, up) with gate/up = W_gate_up[e] * xg[p]: one work item = one tile x 128
+//                       intermediate columns = two accumulators (128 gate rows and the matching 128 up rows), so that a
+//                       thread of the epilogue holds gate and up of the same output.
+//   ffn_umma_kernel<1>  partial[slot, n] = W_down[e] * hs[p]: one work item = one tile x 256 output rows.
+//
+// One CTA per SM walks its work items. Roles:
+//   warp 12     TMA producer: packed 4-bit codes (boxes of 128 rows x 64 bytes, 64-byte swizzle) into a 3-deep ring of
+//               raw stages, token tiles (128 rows x 64 F16, 128-byte swizzle) into the 3-deep operand ring.
+//   warps 0-7   dequantizers: thread = one weight row; per raw stage it turns 128 codes into F16 code * s + m (lop3
+//               "1024 + code", exact subtract, one F16 FMA) and stores them in the K-major 128-byte-swizzled layout the
+//               tensor core reads. Both operands keep each 8 K elements in the order 0,4,1,5,2,6,3,7 (what the nibble
+//               unpack produces); xg and hs are written in that order.
+//   warp 13     allocates all 512 tensor-memory columns (two buffers of two 128-column accumulators) and issues
+//               tcgen05.mma (cta_group::1, kind::f16, FP32 accumulation); tcgen05.commit frees operand stages and
+//               publishes finished accumulators.
+//   warps 8-11  epilogue: tcgen05.ld (lane = weight row, column = routed slot) of one buffer while the next work item
+//               accumulates in the other.
+// Every mbarrier wait is bounded: on expiry the CTA raises the abort counter, frees its tensor memory and returns.
+#include <cuda.h>
+#include <cuda_fp16.h>
+
+#include <algorithm>
+#include <mutex>
+
+#include "prefill_umma.cuh"
+#include "umma.cuh"
+
+namespace {
+
+using namespace sb;
+using namespace sb::umma;
+
+__device__ unsigned int g_prefill_aborts = 0;
+
+constexpr int kBK = 64;                 // K per operand stage: 64 F16 = one 128-byte swizzle row
+constexpr int kTile = kTileM * kBK * 2;  // 16 KB: 128 rows x 64 F16
+constexpr int kS = 3;                   // operand stages: [A0 | A1 | B]
+constexpr int kStage = 3 * kTile;
+constexpr int kRS = 3;                  // raw stages: 2 x (128 rows x 64 bytes) = 128 codes of 256 rows
+constexpr int kRawTile = kTileM * 64;
+constexpr int kRawStage = 2 * kRawTile;
+constexpr int kThreads = 14 * 32;
+constexpr int kTileSlots = 128;
+
+struct Ctl {
+    uint64_t raw_full[kRS], raw_empty[kRS], a_full[kS], b_full[kS], ab_empty[kS], acc_full[2], acc_empty[2];
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+// ---------------------------------------------------------------------------------------------------------------
+// tiles[0] = number of tiles, then (bucket, first sorted position, slots) per tile; buckets in ascending order.
+__global__ void __launch_bounds__(1024) tiles_kernel(const int32_t *ws, int32_t *tiles) {
+    __shared__ int32_t scan[1024];
+    const int32_t S = ws[1], E = ws[2];
+    const RouteTables rt = route_tables(ws, S, E);
+    const int e = threadIdx.x;
+    const int32_t cnt = e < E ? rt.offsets[e + 1] - rt.offsets[e] : 0;
+    const int32_t nt = (cnt + kTileSlots - 1) / kTileSlots;
+    scan[e] = nt;
+    __syncthreads();
+    for (int off = 1; off < 1024; off <<= 1) {
+        const int32_t v = e >= off ? scan[e - off] : 0;
+        __syncthreads();
+        scan[e] += v;
+        __syncthreads();
+    }
+    const int32_t first = scan[e] - nt;
+    for (int t = 0; t < nt; ++t) {
+        int32_t *o = tiles + 1 + 3 * (first + t);
+        o[0] = e, o[1] = rt.offsets[e] + t * kTileSlots, o[2] = min(kTileSlots, cnt - t * kTileSlots);
+    }
+    if (e == 1023) tiles[0] = scan[1023];
+}
+
+// One warp per sorted position p < offsets[E] (the slots with a valid expert).
+template <typename T>
+__global__ void __launch_bounds__(256) pregather_kernel(const T *x, const int32_t *ws, int64_t A, int64_t K, uint16_t *xg) {
+    const int32_t S = ws[1], E = ws[2];
+    const RouteTables rt = route_tables(ws, S, E);
+    const int32_t total = rt.offsets[E];
+    const int lane = threadIdx.x & 31;
+    for (int64_t p = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5); p < total; p += (int64_t)gridDim.x * 8) {
+        const T *src = x + (int64_t)(rt.slots[p] / A) * K;
+        uint4 *dst = reinterpret_cast<uint4 *>(xg + p * K);
+        for (int c = lane; c < K / 8; c += 32) dst[c] = act_chunk(src + c * 8);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+struct FfnArgs {
+    const int32_t *ws, *tiles;
+    const uint16_t *scale, *minv;  // [stack rows, K / G]
+    int K, rows_per_expert, I, RB;
+    uint16_t *hs;    // MODE 0 output: [S, I] F16, 8-groups in the order 0,4,1,5,2,6,3,7
+    float *partial;  // MODE 1 output: [S, N] by slot
+    int N;
+    int bf16_act;    // MODE 0: round gate, up and the product as a BF16 activation pipeline does
+};
+
+__device__ __forceinline__ float swiglu_rounded(float g, float u, bool bf16) {
+    if (bf16) {
+        g = bf16_bits_to_f32(f32_to_bf16_bits(g)), u = bf16_bits_to_f32(f32_to_bf16_bits(u));
+        return bf16_bits_to_f32(f32_to_bf16_bits(bf16_bits_to_f32(f32_to_bf16_bits(silu_f(g))) * u));
+    }
+    return silu_f(g) * u;
+}
+
+template <int MODE, int G>
+__global__ void __launch_bounds__(kThreads, 1)
+    ffn_umma_kernel(const __grid_constant__ CUtensorMap raw_map, const __grid_constant__ CUtensorMap b_map, const FfnArgs a) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t *base = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    uint8_t *stages = base, *raws = base + kS * kStage;
+    Ctl &ctl = *reinterpret_cast<Ctl *>(raws + kRS * kRawStage);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid == 0) {
+        for (int i = 0; i < kRS; ++i) mbar_init(&ctl.raw_full[i], 1), mbar_init(&ctl.raw_empty[i], 8);
+        for (int i = 0; i < kS; ++i) mbar_init(&ctl.a_full[i], 8), mbar_init(&ctl.b_full[i], 1), mbar_init(&ctl.ab_empty[i], 1);
+        for (int i = 0; i < 2; ++i) mbar_init(&ctl.acc_full[i], 1), mbar_init(&ctl.acc_empty[i], 4);
+        ctl.abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 13) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctl.tmem_base)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = ctl.tmem_base;
+    const int n_work = a.tiles[0] * a.RB;
+    const int nkb = a.K / kBK;
+    volatile int *abort_flag = &ctl.abort_flag;
+
+    // stack row of accumulator `acc`, row 0, of work item w
+    auto first_row = [&](int bucket, int rb, int acc) {
+        return MODE == 0 ? bucket * a.rows_per_expert + acc * a.I + rb * kTileM : bucket * a.rows_per_expert + rb * 2 * kTileM + acc * kTileM;
+    };
+
+    if (warp == 12) {
+        // ---- TMA producer ----
+        if (lane == 0) {
+            uint32_t rawc = 0, abc = 0;
+            bool ok = true;
+            for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
+                const int32_t *t = a.tiles + 1 + 3 * (w / a.RB);
+                const int rb = w % a.RB, bucket = t[0], start = t[1];
+                const int r0 = first_row(bucket, rb, 0), r1 = first_row(bucket, rb, 1);
+                for (int kb = 0; kb < nkb && ok; ++kb) {
+                    if ((kb & 1) == 0) {
+                        const int rs = rawc % kRS;
+                        ok = mbar_wait(&ctl.raw_empty[rs], ((rawc / kRS) & 1u) ^ 1u, abort_flag);
+                        if (!ok) break;
+                        mbar_expect_tx(&ctl.raw_full[rs], kRawStage);
+                        tma_load_2d(raws + rs * kRawStage, &raw_map, (kb >> 1) * 64, r0, &ctl.raw_full[rs]);
+                        tma_load_2d(raws + rs * kRawStage + kRawTile, &raw_map, (kb >> 1) * 64, r1, &ctl.raw_full[rs]);
+                        ++rawc;
+                    }
+                    const int s = abc % kS;
+                    ok = mbar_wait(&ctl.ab_empty[s], ((abc / kS) & 1u) ^ 1u, abort_flag);
+                    if (!ok) break;
+                    mbar_expect_tx(&ctl.b_full[s], kTile);
+                    tma_load_2d(stages + s * kStage + 2 * kTile, &b_map, kb * kBK, start, &ctl.b_full[s]);
+                    ++abc;
+                }
+            }
+        }
+    } else if (warp == 13) {
+        // ---- MMA issuer ----
+        uint32_t abc = 0, it = 0;
+        bool ok = true;
+        for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x, ++it) {
+            const int32_t *t = a.tiles + 1 + 3 * (w / a.RB);
+            const int n_mma = (t[2] + 15) & ~15;
+            const uint32_t idesc = umma_idesc(n_mma);
+            const uint32_t buf = it & 1u;
+            if (lane == 0) ok = mbar_wait(&ctl.acc_empty[buf], ((it >> 1) & 1u) ^ 1u, abort_flag);
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) break;
+            tc_fence_after();
+            for (int kb = 0; kb < nkb && ok; ++kb, ++abc) {
+                const int s = abc % kS;
+                const uint32_t ph = (abc / kS) & 1u;
+                if (lane == 0) ok = mbar_wait(&ctl.a_full[s], ph, abort_flag) && mbar_wait(&ctl.b_full[s], ph, abort_flag);
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) break;
+                tc_fence_after();
+                if (lane == 0) {
+                    const uint32_t a0 = smem_u32(stages + s * kStage), b0 = a0 + 2 * kTile;
+#pragma unroll
+                    for (int acc = 0; acc < 2; ++acc)
+#pragma unroll
+                        for (int k = 0; k < kBK / 16; ++k)
+                            umma_f16(tmem + buf * 256 + acc * 128, umma_desc(a0 + acc * kTile + k * 32), umma_desc(b0 + k * 32), idesc,
+                                     (kb | k) ? 1u : 0u);
+                    umma_commit(&ctl.ab_empty[s]);
+                }
+                __syncwarp();
+            }
+            if (lane == 0 && ok) umma_commit(&ctl.acc_full[buf]);
+            __syncwarp();
+        }
+        tc_fence_before();
+    } else if (warp < 8) {
+        // ---- dequantizers: thread = accumulator tid / 128, row tid % 128 ----
+        const int acc = tid >> 7, r = tid & 127;
+        const int gpr = a.K / G;
+        constexpr int NG = 128 / G;  // groups per raw stage (128 codes)
+        uint32_t rawc = 0, abc = 0;
+        bool ok = true;
+        for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
+            const int32_t *t = a.tiles + 1 + 3 * (w / a.RB);
+            const int64_t row = (int64_t)first_row(t[0], w % a.RB, acc) + r;
+            const uint16_t *srow = a.scale + row * gpr, *mrow = a.minv + row * gpr;
+            for (int kb2 = 0; kb2 < nkb / 2 && ok; ++kb2, ++rawc) {
+                uint32_t s2[NG], m2[NG];
+#pragma unroll
+                for (int g = 0; g < NG; ++g) s2[g] = bf16_to_h2(__ldg(srow + kb2 * NG + g)), m2[g] = bf16_to_h2(__ldg(mrow + kb2 * NG + g));
+                const int rs = rawc % kRS;
+                ok = mbar_wait(&ctl.raw_full[rs], (rawc / kRS) & 1u, abort_flag);
+                if (!ok) break;
+                const uint8_t *rt = raws + rs * kRawStage + acc * kRawTile + r * 64;
+                uint4 c[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) c[j] = *reinterpret_cast<const uint4 *>(rt + ((j ^ ((r >> 1) & 3)) << 4));
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&ctl.raw_empty[rs]);  // the codes are in registers
+#pragma unroll
+                for (int kbl = 0; kbl < 2; ++kbl, ++abc) {
+                    const int s = abc % kS;
+                    ok = mbar_wait(&ctl.ab_empty[s], ((abc / kS) & 1u) ^ 1u, abort_flag);
+                    if (!ok) break;
+                    uint8_t *ta = stages + s * kStage + acc * kTile;
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        const uint4 q = c[kbl * 2 + (u >> 2)];
+                        const uint32_t wv = (u & 3) == 0 ? q.x : (u & 3) == 1 ? q.y : (u & 3) == 2 ? q.z : q.w;
+                        const int g = (kbl * 64 + u * 8) / G;
+                        st_chunk(ta, r, u, dequant_word4(wv, s2[g], m2[g]));
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&ctl.a_full[s]);
+                }
+            }
+        }
+    } else {
+        // ---- epilogue: warps 8..11, lane quadrant q = warp - 8 ----
+        const int q = warp - 8, r = q * 32 + lane;
+        const RouteTables rtab = route_tables(a.ws, a.ws[1], a.ws[2]);
+        uint32_t it = 0;
+        bool ok = true;
+        for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x, ++it) {
+            const int32_t *t = a.tiles + 1 + 3 * (w / a.RB);
+            const int rb = w % a.RB, start = t[1], n_valid = t[2];
+            const uint32_t buf = it & 1u;
+            ok = mbar_wait(&ctl.acc_full[buf], (it >> 1) & 1u, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t tbase = tmem + ((uint32_t)(q * 32) << 16) + buf * 256;
+            for (int c0 = 0; c0 < n_valid; c0 += 32) {
+                uint32_t v0[32], v1[32];
+                tmem_ld32(tbase + c0, v0);
+                tmem_ld32(tbase + 128 + c0, v1);
+                tmem_ld_wait();
+                if (MODE == 0) {
+                    const int i = rb * kTileM + r;  // intermediate column
+                    const int pos = (i & ~7) + ((i & 3) << 1) + ((i >> 2) & 1);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        if (c0 + j < n_valid) {
+                            const float h = swiglu_rounded(__uint_as_float(v0[j]), __uint_as_float(v1[j]), a.bf16_act != 0);
+                            a.hs[(int64_t)(start + c0 + j) * a.I + pos] = __half_as_ushort(__float2half_rn(h));
+                        }
+                    }
+                } else {
+                    const int n = rb * 2 * kTileM + r;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        if (c0 + j < n_valid) {
+                            float *dst = a.partial + (int64_t)rtab.slots[start + c0 + j] * a.N + n;
+                            dst[0] = __uint_as_float(v0[j]);
+                            dst[kTileM] = __uint_as_float(v1[j]);
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&ctl.acc_empty[buf]);
+        }
+    }
+    __syncthreads();
+    if (tid == 0 && ctl.abort_flag) atomicAdd(&g_prefill_aborts, 1u);
+    if (warp == 13) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// logits[m, r] = sum_k x[m, k] * w[r, k], BF16 operands straight from global memory. Grid (row tiles, token tiles).
+constexpr int kDS = 4;  // stages of [A 16 KB | B 16 KB]
+struct DenseCtl {
+    uint64_t full[kDS], empty[kDS], acc_full;
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+__global__ void __launch_bounds__(192, 1)
+    dense_umma_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap x_map, int K, int R, int M, float *logits) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t *stages = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    DenseCtl &ctl = *reinterpret_cast<DenseCtl *>(stages + kDS * 2 * kTile);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid == 0) {
+        for (int i = 0; i < kDS; ++i) mbar_init(&ctl.full[i], 1), mbar_init(&ctl.empty[i], 1);
+        mbar_init(&ctl.acc_full, 1);
+        ctl.abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 5) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctl.tmem_base)), "r"(128u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = ctl.tmem_base;
+    const int r0 = blockIdx.x * kTileM, m0 = blockIdx.y * 128;
+    const int nkb = K / kBK;
+    volatile int *abort_flag = &ctl.abort_flag;
+    if (warp == 4) {
+        if (lane == 0) {
+            for (int kb = 0; kb < nkb; ++kb) {
+                const int s = kb % kDS;
+                if (!mbar_wait(&ctl.empty[s], ((kb / kDS) & 1u) ^ 1u, abort_flag)) break;
+                mbar_expect_tx(&ctl.full[s], 2 * kTile);
+                tma_load_2d(stages + s * 2 * kTile, &w_map, kb * kBK, r0, &ctl.full[s]);
+                tma_load_2d(stages + s * 2 * kTile + kTile, &x_map, kb * kBK, m0, &ctl.full[s]);
+            }
+        }
+    } else if (warp == 5) {
+        const uint32_t idesc = umma_idesc(128, /*bf16=*/true);
+        bool ok = true;
+        for (int kb = 0; kb < nkb && ok; ++kb) {
+            const int s = kb % kDS;
+            if (lane == 0) ok = mbar_wait(&ctl.full[s], (kb / kDS) & 1u, abort_flag);
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) break;
+            tc_fence_after();
+            if (lane == 0) {
+                const uint32_t a0 = smem_u32(stages + s * 2 * kTile), b0 = a0 + kTile;
+#pragma unroll
+                for (int k = 0; k < kBK / 16; ++k) umma_f16(tmem, umma_desc(a0 + k * 32), umma_desc(b0 + k * 32), idesc, (kb | k) ? 1u : 0u);
+                umma_commit(&ctl.empty[s]);
+            }
+            __syncwarp();
+        }
+        if (lane == 0 && ok) umma_commit(&ctl.acc_full);
+        tc_fence_before();
+    } else {
+        if (mbar_wait(&ctl.acc_full, 0, abort_flag)) {
+            tc_fence_after();
+            const int r = r0 + warp * 32 + lane;
+            for (int c0 = 0; c0 < 128 && m0 + c0 < M; c0 += 32) {
+                uint32_t v[32];
+                tmem_ld32(tmem + ((uint32_t)(warp * 32) << 16) + c0, v);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    if (r < R && m0 + c0 + j < M) logits[(int64_t)(m0 + c0 + j) * R + r] = __uint_as_float(v[j]);
+            }
+        }
+        tc_fence_before();
+    }
+    __syncthreads();
+    if (tid == 0 && ctl.abort_flag) atomicAdd(&g_prefill_aborts, 1u);
+    if (warp == 5) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(128u) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+using EncodeFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                              const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+int encoder(const char *fn, EncodeFn *out) {
+    static std::mutex mu;
+    static EncodeFn cached = nullptr;
+    std::lock_guard<std::mutex> lock(mu);
+    if (cached == nullptr) {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        SB_CUDA(cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &p, 12000, cudaEnableDefault, &q), fn, ": looking up the tensor-map encoder");
+        SB_CHECK(q == cudaDriverEntryPointSuccess && p != nullptr, fn, ": the driver has no tensor-map encoder");
+        cached = reinterpret_cast<EncodeFn>(p);
+    }
+    *out = cached;
+    return 0;
+}
+
+// rows x cols elements of `es` bytes, row pitch = cols * es, box = 128 rows x box_cols.
+int make_map(const char *fn, CUtensorMap *m, CUtensorMapDataType dt, int es, const void *ptr, int64_t rows, int64_t cols, int box_cols,
+             CUtensorMapSwizzle sw) {
+    EncodeFn enc;
+    SB_TRY(encoder(fn, &enc));
+    SB_CHECK(reinterpret_cast<uintptr_t>(ptr) % 16 == 0 && (cols * es) % 16 == 0, fn, ": tensor ", ptr, " with a row pitch of ", cols * es,
+             " bytes is not 16-byte aligned");
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows}, strides[1] = {(cuuint64_t)(cols * es)};
+    const cuuint32_t box[2] = {(cuuint32_t)box_cols, 128}, estr[2] = {1, 1};
+    const CUresult rc = enc(m, dt, 2, const_cast<void *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    SB_CHECK(rc == CUDA_SUCCESS, fn, ": cuTensorMapEncodeTiled failed with ", (int)rc, " for a [", rows, ", ", cols, "] tensor");
+    return 0;
+}
+
+constexpr size_t kFfnSmem = (size_t)kS * kStage + (size_t)kRS * kRawStage + sizeof(Ctl) + 1024;
+constexpr size_t kDenseSmem = (size_t)kDS * 2 * kTile + sizeof(DenseCtl) + 1024;
+
+template <int MODE>
+int launch_ffn(const char *fn, int G, const CUtensorMap &raw, const CUtensorMap &b, const FfnArgs &a, int ctas, cudaStream_t st) {
+    static thread_local int prepared = -1;  // one per MODE and host thread
+    int dev = 0;
+    SB_CUDA(cudaGetDevice(&dev), fn);
+    if (prepared != dev) {
+        SB_CUDA(cudaFuncSetAttribute(ffn_umma_kernel<MODE, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kFfnSmem), fn);
+        SB_CUDA(cudaFuncSetAttribute(ffn_umma_kernel<MODE, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kFfnSmem), fn);
+        SB_CUDA(cudaFuncSetAttribute(ffn_umma_kernel<MODE, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kFfnSmem), fn);
+        prepared = dev;
+    }
+    if (G == 32) ffn_umma_kernel<MODE, 32><<<ctas, kThreads, kFfnSmem, st>>>(raw, b, a);
+    else if (G == 64) ffn_umma_kernel<MODE, 64><<<ctas, kThreads, kFfnSmem, st>>>(raw, b, a);
+    else ffn_umma_kernel<MODE, 128><<<ctas, kThreads, kFfnSmem, st>>>(raw, b, a);
+    SB_LAUNCH_OK(fn, " (tcgen05 FFN stage ", MODE, ") K=", a.K, " G=", G);
+    return 0;
+}
+
+}  // namespace
+
+namespace sb {
+
+struct PrefillPlan {
+    CUtensorMap gu_raw, dn_raw, xg_map, hs_map, rw_map;
+    bool dense_router = false;
+    int64_t d, I, Estack, max_tokens, A, router_rows;
+    int G_gu, G_dn;
+    const uint16_t *gu_scale, *gu_min, *dn_scale, *dn_min;
+    uint16_t *xg = nullptr, *hs = nullptr;
+    int32_t *tiles = nullptr;
+    int sms = 0;
+};
+
+bool prefill_supported(const strix_moe_layer_desc &d) {
+    return !d.experts_mixed && d.gate_up_bits == 4 && d.down_bits == 4 && d.d % 256 == 0 && d.I % 128 == 0 && d.d <= (1 << 20) && d.I <= (1 << 20);
+}
+
+int prefill_create(const strix_moe_layer_desc &d, int64_t A, int64_t Estack, int64_t router_rows, PrefillPlan **out) {
+    const char *fn = "moe_layer_create (tensor-core path)";
+    auto *p = new PrefillPlan();
+    p->d = d.d, p->I = d.I, p->Estack = Estack, p->max_tokens = d.max_tokens, p->A = A, p->router_rows = router_rows;
+    p->G_gu = (int)d.gate_up.G, p->G_dn = (int)d.down.G;
+    p->gu_scale = d.gate_up.scale, p->gu_min = d.gate_up.minv, p->dn_scale = d.down.scale, p->dn_min = d.down.minv;
+    p->sms = sm_count();
+    const int64_t S = d.max_tokens * A;
+    int rc = 0;
+    auto alloc = [&](void **q, size_t bytes) {
+        if (rc == 0 && cudaMalloc(q, bytes) != cudaSuccess) {
+            last_error() = std::string(fn) + ": cudaMalloc failed";
+            rc = STRIX_ERR_CUDA;
+        }
+    };
+    alloc(reinterpret_cast<void **>(&p->xg), (size_t)S * d.d * 2);
+    alloc(reinterpret_cast<void **>(&p->hs), (size_t)S * d.I * 2);
+    alloc(reinterpret_cast<void **>(&p->tiles), (size_t)(1 + 3 * (S / kTileSlots + Estack + 2)) * 4);
+    if (rc == 0) rc = make_map(fn, &p->gu_raw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, d.gate_up.q, Estack * 2 * d.I, d.d / 2, 64, CU_TENSOR_MAP_SWIZZLE_64B);
+    if (rc == 0) rc = make_map(fn, &p->dn_raw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, d.down.q, Estack * d.d, d.I / 2, 64, CU_TENSOR_MAP_SWIZZLE_64B);
+    if (rc == 0) rc = make_map(fn, &p->xg_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, p->xg, S, d.d, kBK, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc == 0) rc = make_map(fn, &p->hs_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, p->hs, S, d.I, kBK, CU_TENSOR_MAP_SWIZZLE_128B);
+    p->dense_router = d.act == kBF16 && d.router_kind == STRIX_ROUTER_BF16 && d.d % kBK == 0;
+    if (rc == 0 && p->dense_router)
+        rc = make_map(fn, &p->rw_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, d.router_w, router_rows, d.d, kBK, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != 0) {
+        prefill_destroy(p);
+        return rc;
+    }
+    *out = p;
+    return 0;
+}
+
+void prefill_destroy(PrefillPlan *p) {
+    if (p == nullptr) return;
+    if (p->xg) cudaFree(p->xg);
+    if (p->hs) cudaFree(p->hs);
+    if (p->tiles) cudaFree(p->tiles);
+    delete p;
+}
+
+bool prefill_has_dense_router(const PrefillPlan *p) { return p->dense_router; }
+
+int prefill_router_logits(PrefillPlan *p, const void *x, int64_t M, float *logits, cudaStream_t st) {
+    const char *fn = "moe_layer_forward (tensor-core router)";
+    CUtensorMap xm;
+    SB_TRY(make_map(fn, &xm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, M, p->d, kBK, CU_TENSOR_MAP_SWIZZLE_128B));
+    static thread_local int prepared = -1;
+    int dev = 0;
+    SB_CUDA(cudaGetDevice(&dev), fn);
+    if (prepared != dev) {
+        SB_CUDA(cudaFuncSetAttribute(dense_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kDenseSmem), fn);
+        prepared = dev;
+    }
+    const dim3 grid((unsigned)((p->router_rows + kTileM - 1) / kTileM), (unsigned)((M + 127) / 128));
+    dense_umma_kernel<<<grid, 192, kDenseSmem, st>>>(p->rw_map, xm, (int)p->d, (int)p->router_rows, (int)M, logits);
+    SB_LAUNCH_OK(fn, " M=", M, " R=", p->router_rows, " K=", p->d);
+    return 0;
+}
+
+int prefill_experts(PrefillPlan *p, const void *x, int act, const int32_t *ws, int64_t M, float *partial, cudaStream_t st) {
+    const char *fn = "moe_layer_forward (tensor-core experts)";
+    tiles_kernel<<<1, 1024, 0, st>>>(ws, p->tiles);
+    SB_LAUNCH_OK(fn, ": tiles");
+    const unsigned gblocks = (unsigned)std::min<int64_t>((M * p->A + 7) / 8, 148 * 16);
+    if (act == kF32) pregather_kernel<float><<<gblocks, 256, 0, st>>>((const float *)x, ws, p->A, p->d, p->xg);
+    else pregather_kernel<uint16_t><<<gblocks, 256, 0, st>>>((const uint16_t *)x, ws, p->A, p->d, p->xg);
+    SB_LAUNCH_OK(fn, ": gather");
+    FfnArgs a{};
+    a.ws = ws, a.tiles = p->tiles;
+    a.scale = p->gu_scale, a.minv = p->gu_min, a.K = (int)p->d, a.rows_per_expert = (int)(2 * p->I), a.I = (int)p->I, a.RB = (int)(p->I / kTileM);
+    a.hs = p->hs, a.partial = nullptr, a.N = 0, a.bf16_act = act == kBF16;
+    SB_TRY(launch_ffn<0>(fn, p->G_gu, p->gu_raw, p->xg_map, a, p->sms, st));
+    a.scale = p->dn_scale, a.minv = p->dn_min, a.K = (int)p->I, a.rows_per_expert = (int)p->d, a.RB = (int)(p->d / (2 * kTileM));
+    a.hs = nullptr, a.partial = partial, a.N = (int)p->d;
+    SB_TRY(launch_ffn<1>(fn, p->G_dn, p->dn_raw, p->hs_map, a, p->sms, st));
+    return 0;
+}
+
+unsigned int prefill_aborts() {
+    unsigned int v = 0;
+    cudaMemcpyFromSymbol(&v, g_prefill_aborts, sizeof(v));
+    return v;
+}
+
+}  // namespace sb

@@ -1,0 +1,29 @@
+// The many-token expert FFN on tcgen05 tensor cores (prefill_umma.cu), as the layer object drives it.
+#pragma once
+
+#include "common.cuh"
+#include "grouped.cuh"
+#include "strixite_b200.h"
+
+namespace sb {
+
+struct PrefillPlan;  // tensor maps of the weight stacks, the bucket-ordered activation buffers and the tile table
+
+// Uniform 4-bit stacks with d % 256 == 0 and I % 128 == 0.
+bool prefill_supported(const strix_moe_layer_desc &d);
+int prefill_create(const strix_moe_layer_desc &d, int64_t A, int64_t Estack, int64_t router_rows, PrefillPlan **out);
+void prefill_destroy(PrefillPlan *p);
+// BF16 activations with a BF16 router: the router projection runs on the tensor cores too.
+bool prefill_has_dense_router(const PrefillPlan *p);
+int prefill_router_logits(PrefillPlan *p, const void *x, int64_t M, float *logits, cudaStream_t st);
+// Tiles -> bucket-ordered F16 activations -> gate/up + SwiGLU -> down: FP32 partial[slot, d] for every slot with a
+// valid expert. `ws` is the grouping workspace of moe_group_routes for (M, A, Estack).
+int prefill_experts(PrefillPlan *p, const void *x, int act, const int32_t *ws, int64_t M, float *partial, cudaStream_t st);
+// CTAs of these kernels that gave up on a bounded wait since the library was loaded.
+unsigned int prefill_aborts();
+
+// y[m, :] = sum_a coef[m, a] * partial[m * A + a, :] in ascending a; NaN rows for tokens with an invalid id (grouped.cu).
+int combine_reduce(const char *fn, const float *partial, const int32_t *ids, const float *coef, int64_t M, int64_t A, int64_t E, int64_t N,
+                   void *y, int act, cudaStream_t st);
+
+}  // namespace sb

@@ -415,6 +415,11 @@ def linear_q4_experts_combine_grouped(h, w, E, ids, coef, ws, ws_bytes, partial,
     _combine_grouped(4, h, w, E, ids, coef, ws, ws_bytes, partial, M, A, y, act, math, stream)
 
 
+def umma_abort_count():
+    """Thread blocks of the tensor-core kernels that abandoned a bounded wait since the library was loaded (0 when healthy)."""
+    return int(lib.strix_umma_abort_count())
+
+
 FIXED_PARTIAL_FLOATS = 1 << 20  # STRIX_FIXED_PARTIAL_FLOATS
 
 

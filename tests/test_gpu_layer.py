@@ -13,9 +13,9 @@ pytestmark = pytest.mark.gpu
 LAYER_TOL = 2e-3  # max |y - y_oracle| / max |y_oracle| per row
 
 
-def run_and_check(L, x, act, grouped_min_tokens=6, max_tokens=None, decode_impl=0):
+def run_and_check(L, x, act, grouped_min_tokens=6, max_tokens=None, decode_impl=0, math=0, bf16_excess=1.0):
     M = x.shape[0]
-    layer = gpu_layer(L, act, max_tokens or M, grouped_min_tokens, decode_impl=decode_impl)
+    layer = gpu_layer(L, act, max_tokens or M, grouped_min_tokens, decode_impl=decode_impl, math=math)
     y = layer.forward(to_torch_act(x))
     torch.cuda.synchronize()
     yref, it = oracle.moe_layer(x, L)
@@ -36,7 +36,11 @@ def run_and_check(L, x, act, grouped_min_tokens=6, max_tokens=None, decode_impl=
     assert np.isfinite(got).all()
     e = rel_err_rows(got[keep], want[keep])
     if act == oracle.BF16:  # the output is rounded to BF16: allow one BF16 step of the element on top of the contract
-        assert bf16_rows_close(got[keep], want[keep], LAYER_TOL) <= 1.0, "layer error %.3g" % e
+        assert bf16_rows_close(got[keep], want[keep], LAYER_TOL) <= bf16_excess, "layer error %.3g" % e
+        if bf16_excess > 1.0:  # nearly every element inside the plain allowance
+            rowmax = np.abs(want[keep]).max(axis=1, keepdims=True)
+            ulp = 2.0 ** (np.floor(np.log2(np.maximum(np.abs(want[keep]), 1e-30))) - 7)
+            assert (np.abs(got[keep] - want[keep]) <= LAYER_TOL * rowmax + ulp).mean() > 0.999
     else:
         assert e < LAYER_TOL, "layer error %.3g" % e
     assert layer.probe("err", M).cpu().numpy().tolist() == [0] * 6
@@ -146,3 +150,28 @@ def test_full_width_properties_config1():
     a = layer.forward(to_torch_act(x)).cpu().numpy()
     b = layer.forward(to_torch_act(x)).cpu().numpy()
     assert np.array_equal(a, b)
+
+
+@pytest.mark.parametrize("act,router", [(oracle.BF16, "bf16"), (oracle.F32, "f32"), (oracle.BF16, "q8")])
+@pytest.mark.parametrize("G,shared,M", [(128, "stacked", 333), (32, "separate", 130), (64, None, 64)])
+def test_prefill_tensor_core_path(act, router, G, shared, M):
+    # config 3 scaled down: many tokens, skewed routing (hot experts span several 128-slot tiles, cold ones get a few slots
+    # or none), q4 experts, the tcgen05 path end to end: tensor-core router (BF16 x BF16), bucket-ordered F16 activations,
+    # gate/up + SwiGLU, down, ordered reduce.
+    import strixite_b200 as sb
+
+    L = make_layer(900 + M, d=512, I=256, E=24, k=4, G=G, router=router, shared=shared, bias_sigma=1.0, shared_bits=8, shared_G=64)
+    x = randn_act(np.random.default_rng(901 + M), (M, 512), act)
+    before = sb.kernels.umma_abort_count()
+    # FP32 activations: F16 operand rounding (2^-12 per value) stays far inside the 2e-3 contract. BF16 activations: the
+    # pipeline rounds gate, up, silu and h to BF16 like the FP32-math path, and a 1e-4 operand-rounding difference
+    # before such a rounding flips it to the neighbouring BF16 value (0.4-0.8 %) in a few percent of the h elements; the
+    # outputs then differ from the oracle's by up to twice the plain allowance in under 0.1 % of the elements.
+    layer, e = run_and_check(L, x, act, math=2, bf16_excess=2.0)
+    if act == oracle.F32:
+        assert e < 1e-3
+    assert sb.kernels.umma_abort_count() == before
+    # twice through the same layer object: the persistent kernels leave no state behind
+    y1 = layer.forward(to_torch_act(x)).clone()
+    y2 = layer.forward(to_torch_act(x))
+    assert torch.equal(y1, y2)
