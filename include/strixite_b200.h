@@ -196,6 +196,10 @@ int strix_linear_q4_experts_combine_grouped_fixed(const void *h, const strix_qvi
 /* Number of thread blocks of the tensor-core grouped GEMM that abandoned a bounded wait since the library was loaded:
  * 0 in a healthy run (their outputs are undefined otherwise). No counterpart in the reference. Synchronizes. */
 unsigned int strix_umma_abort_count(void);
+/* Diagnostics of the many-token tensor-core kernels: clock cycles their warp roles spent waiting on each other, summed
+ * over thread blocks since the last reset; out32 = 2 kernels x 16 counters (index list in csrc/prefill_umma.cu).
+ * No counterpart in the reference. Synchronizes. */
+void strix_umma_wait_cycles(unsigned long long *out32, int reset);
 /* The grouped pair over a stack with a format per expert. No counterpart in the reference. */
 int strix_linear_qmix_experts_gather_grouped(const void *x, const strix_qmix_view *w, const void *ws, size_t ws_bytes,
                                              int64_t M, int64_t A, void *y, int act, int math, void *stream);

@@ -337,6 +337,7 @@ int mixed_view(const char *fn, const strix_qmix_view *w, StackView *out) {
 extern "C" {
 
 unsigned int strix_umma_abort_count(void) { return sb::grouped_umma_aborts() + sb::prefill_aborts(); }
+void strix_umma_wait_cycles(unsigned long long *out32, int reset) { sb::prefill_cycles(out32, reset != 0); }
 
 size_t strix_moe_route_workspace_bytes(int64_t M, int64_t A, int64_t E) {
     int64_t ints = 0;

@@ -11,20 +11,24 @@
 //                       thread of the epilogue holds gate and up of the same output.
 //   ffn_umma_kernel<1>  partial[slot, n] = W_down[e] * hs[p]: one work item = one tile x 256 output rows.
 //
-// One CTA per SM walks its work items. Roles:
-//   warp 12     TMA producer: packed 4-bit codes (boxes of 128 rows x 64 bytes, 64-byte swizzle) into a 3-deep ring of
-//               raw stages, token tiles (128 rows x 64 F16, 128-byte swizzle) into the 3-deep operand ring.
-//   warps 0-7   dequantizers: thread = one weight row; per raw stage it turns 128 codes into F16 code * s + m (lop3
-//               "1024 + code", exact subtract, one F16 FMA) and stores them in the K-major 128-byte-swizzled layout the
-//               tensor core reads. Both operands keep each 8 K elements in the order 0,4,1,5,2,6,3,7 (what the nibble
-//               unpack produces); xg and hs are written in that order.
-//   warp 13     allocates all 512 tensor-memory columns (two buffers of two 128-column accumulators) and issues
+// One CTA per SM walks its work items (26 warps). Roles:
+//   warp 24     TMA producer: packed 4-bit codes (boxes of 128 rows x 64 bytes, 64-byte swizzle) into a 3-deep ring of
+//               raw stages, token tiles (128 rows x 64 F16, 128-byte swizzle) into a 4-deep ring.
+//   warps 0-15  dequantizers: thread = 64 codes of one weight row per raw stage -> F16 code * s + m (lop3
+//               "1024 + code", exact subtract, one F16 FMA) stored in the K-major 128-byte-swizzled layout the tensor
+//               core reads (3-deep ring of [A0 | A1]). Both operands keep each 8 K elements in the order
+//               0,4,1,5,2,6,3,7 (what the nibble unpack produces); xg and hs are written in that order.
+//   warp 25     allocates all 512 tensor-memory columns (two buffers of two 128-column accumulators) and issues
 //               tcgen05.mma (cta_group::1, kind::f16, FP32 accumulation); tcgen05.commit frees operand stages and
 //               publishes finished accumulators.
-//   warps 8-11  epilogue: tcgen05.ld (lane = weight row, column = routed slot) of one buffer while the next work item
+//   warps 16-23 epilogue: tcgen05.ld (lane = weight row, column = routed slot) of one buffer while the next work item
 //               accumulates in the other.
 // Every mbarrier wait is bounded: on expiry the CTA raises the abort counter, frees its tensor memory and returns.
+// What bounds it: shared-memory bandwidth. Per K block the tensor core reads 32 KB of A and twice the token tile, the
+// dequantizers write those 32 KB and read 16 KB of codes, TMA writes 32 KB: ~130 KB at 128 bytes per clock is about twice
+// the MMA time at 80 tokens per expert.
 #include <cuda.h>
+#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
 #include <algorithm>
@@ -39,19 +43,33 @@ using namespace sb;
 using namespace sb::umma;
 
 __device__ unsigned int g_prefill_aborts = 0;
+// Cycles the roles of the FFN kernels spent in their waits, summed over CTAs since the last reset (diagnostics):
+// [mode * 16 + i], i = 0 kernel total, 1 producer raw_empty, 2 producer ab_empty, 3 mma acc_empty, 4 mma a_full, 5 mma b_full,
+// 6 dequant raw_full, 7 dequant ab_empty, 8 dequant total, 9 epilogue acc_full, 10 epilogue total, 11 work items.
+__device__ unsigned long long g_prefill_cycles[32];
+
+#define TIMED_WAIT(slot, expr)                 \
+    do {                                       \
+        const long long t0_ = clock64();       \
+        ok = (expr);                           \
+        waited[slot] += clock64() - t0_;       \
+    } while (0)
 
 constexpr int kBK = 64;                 // K per operand stage: 64 F16 = one 128-byte swizzle row
 constexpr int kTile = kTileM * kBK * 2;  // 16 KB: 128 rows x 64 F16
-constexpr int kS = 3;                   // operand stages: [A0 | A1 | B]
-constexpr int kStage = 3 * kTile;
+constexpr int kAS = 3;                  // A stages: [A0 | A1], two accumulators' weight tiles of one K block
+constexpr int kAStage = 2 * kTile;
+constexpr int kBS = 4;                  // B stages: the token tile of one K block
 constexpr int kRS = 3;                  // raw stages: 2 x (128 rows x 64 bytes) = 128 codes of 256 rows
 constexpr int kRawTile = kTileM * 64;
 constexpr int kRawStage = 2 * kRawTile;
-constexpr int kThreads = 14 * 32;
+constexpr int kDequantWarps = 16, kEpilogueWarps = 8;
+constexpr int kProducerWarp = kDequantWarps + kEpilogueWarps, kMmaWarp = kProducerWarp + 1;
+constexpr int kThreads = (kMmaWarp + 1) * 32;
 constexpr int kTileSlots = 128;
 
 struct Ctl {
-    uint64_t raw_full[kRS], raw_empty[kRS], a_full[kS], b_full[kS], ab_empty[kS], acc_full[2], acc_empty[2];
+    uint64_t raw_full[kRS], raw_empty[kRS], a_full[kAS], a_empty[kAS], b_full[kBS], b_empty[kBS], acc_full[2], acc_empty[2];
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -106,12 +124,14 @@ struct FfnArgs {
     int bf16_act;    // MODE 0: round gate, up and the product as a BF16 activation pipeline does
 };
 
+__device__ __forceinline__ float bf16_rn(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+// SwiGLU of one output; a BF16 activation pipeline rounds gate, up, silu(gate) and the product (strixite kernels/swiglu.hpp:21).
 __device__ __forceinline__ float swiglu_rounded(float g, float u, bool bf16) {
     if (bf16) {
-        g = bf16_bits_to_f32(f32_to_bf16_bits(g)), u = bf16_bits_to_f32(f32_to_bf16_bits(u));
-        return bf16_bits_to_f32(f32_to_bf16_bits(bf16_bits_to_f32(f32_to_bf16_bits(silu_f(g))) * u));
+        g = bf16_rn(g), u = bf16_rn(u);
+        return bf16_rn(bf16_rn(__fdividef(g, 1.0f + __expf(-g))) * u);
     }
-    return silu_f(g) * u;
+    return __fdividef(g, 1.0f + __expf(-g)) * u;
 }
 
 template <int MODE, int G>
@@ -119,17 +139,19 @@ __global__ void __launch_bounds__(kThreads, 1)
     ffn_umma_kernel(const __grid_constant__ CUtensorMap raw_map, const __grid_constant__ CUtensorMap b_map, const FfnArgs a) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t *base = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-    uint8_t *stages = base, *raws = base + kS * kStage;
+    uint8_t *a_stages = base, *b_stages = base + kAS * kAStage, *raws = b_stages + kBS * kTile;
     Ctl &ctl = *reinterpret_cast<Ctl *>(raws + kRS * kRawStage);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const long long t_kernel = clock64();
     if (tid == 0) {
-        for (int i = 0; i < kRS; ++i) mbar_init(&ctl.raw_full[i], 1), mbar_init(&ctl.raw_empty[i], 8);
-        for (int i = 0; i < kS; ++i) mbar_init(&ctl.a_full[i], 8), mbar_init(&ctl.b_full[i], 1), mbar_init(&ctl.ab_empty[i], 1);
-        for (int i = 0; i < 2; ++i) mbar_init(&ctl.acc_full[i], 1), mbar_init(&ctl.acc_empty[i], 4);
+        for (int i = 0; i < kRS; ++i) mbar_init(&ctl.raw_full[i], 1), mbar_init(&ctl.raw_empty[i], kDequantWarps);
+        for (int i = 0; i < kAS; ++i) mbar_init(&ctl.a_full[i], kDequantWarps / 2), mbar_init(&ctl.a_empty[i], 1);
+        for (int i = 0; i < kBS; ++i) mbar_init(&ctl.b_full[i], 1), mbar_init(&ctl.b_empty[i], 1);
+        for (int i = 0; i < 2; ++i) mbar_init(&ctl.acc_full[i], 1), mbar_init(&ctl.acc_empty[i], kEpilogueWarps);
         ctl.abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 13) {
+    if (warp == kMmaWarp) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctl.tmem_base)), "r"(512u) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -141,16 +163,17 @@ __global__ void __launch_bounds__(kThreads, 1)
     const int nkb = a.K / kBK;
     volatile int *abort_flag = &ctl.abort_flag;
 
-    // stack row of accumulator `acc`, row 0, of work item w
+    // stack row of accumulator `acc`, row 0, of a work item
     auto first_row = [&](int bucket, int rb, int acc) {
         return MODE == 0 ? bucket * a.rows_per_expert + acc * a.I + rb * kTileM : bucket * a.rows_per_expert + rb * 2 * kTileM + acc * kTileM;
     };
 
-    if (warp == 12) {
+    if (warp == kProducerWarp) {
         // ---- TMA producer ----
         if (lane == 0) {
-            uint32_t rawc = 0, abc = 0;
+            uint32_t rawc = 0, bc = 0;
             bool ok = true;
+            long long waited[2] = {0, 0};
             for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
                 const int32_t *t = a.tiles + 1 + 3 * (w / a.RB);
                 const int rb = w % a.RB, bucket = t[0], start = t[1];
@@ -158,125 +181,141 @@ __global__ void __launch_bounds__(kThreads, 1)
                 for (int kb = 0; kb < nkb && ok; ++kb) {
                     if ((kb & 1) == 0) {
                         const int rs = rawc % kRS;
-                        ok = mbar_wait(&ctl.raw_empty[rs], ((rawc / kRS) & 1u) ^ 1u, abort_flag);
+                        TIMED_WAIT(0, mbar_wait(&ctl.raw_empty[rs], ((rawc / kRS) & 1u) ^ 1u, abort_flag));
                         if (!ok) break;
                         mbar_expect_tx(&ctl.raw_full[rs], kRawStage);
                         tma_load_2d(raws + rs * kRawStage, &raw_map, (kb >> 1) * 64, r0, &ctl.raw_full[rs]);
                         tma_load_2d(raws + rs * kRawStage + kRawTile, &raw_map, (kb >> 1) * 64, r1, &ctl.raw_full[rs]);
                         ++rawc;
                     }
-                    const int s = abc % kS;
-                    ok = mbar_wait(&ctl.ab_empty[s], ((abc / kS) & 1u) ^ 1u, abort_flag);
+                    const int s = bc % kBS;
+                    TIMED_WAIT(1, mbar_wait(&ctl.b_empty[s], ((bc / kBS) & 1u) ^ 1u, abort_flag));
                     if (!ok) break;
                     mbar_expect_tx(&ctl.b_full[s], kTile);
-                    tma_load_2d(stages + s * kStage + 2 * kTile, &b_map, kb * kBK, start, &ctl.b_full[s]);
-                    ++abc;
+                    tma_load_2d(b_stages + s * kTile, &b_map, kb * kBK, start, &ctl.b_full[s]);
+                    ++bc;
                 }
             }
+            atomicAdd(&g_prefill_cycles[MODE * 16 + 1], (unsigned long long)waited[0]);
+            atomicAdd(&g_prefill_cycles[MODE * 16 + 2], (unsigned long long)waited[1]);
         }
-    } else if (warp == 13) {
+    } else if (warp == kMmaWarp) {
         // ---- MMA issuer ----
-        uint32_t abc = 0, it = 0;
+        uint32_t kc = 0, it = 0;
         bool ok = true;
+        long long waited[3] = {0, 0, 0};
         for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x, ++it) {
             const int32_t *t = a.tiles + 1 + 3 * (w / a.RB);
             const int n_mma = (t[2] + 15) & ~15;
             const uint32_t idesc = umma_idesc(n_mma);
             const uint32_t buf = it & 1u;
-            if (lane == 0) ok = mbar_wait(&ctl.acc_empty[buf], ((it >> 1) & 1u) ^ 1u, abort_flag);
+            if (lane == 0) TIMED_WAIT(0, mbar_wait(&ctl.acc_empty[buf], ((it >> 1) & 1u) ^ 1u, abort_flag));
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) break;
             tc_fence_after();
-            for (int kb = 0; kb < nkb && ok; ++kb, ++abc) {
-                const int s = abc % kS;
-                const uint32_t ph = (abc / kS) & 1u;
-                if (lane == 0) ok = mbar_wait(&ctl.a_full[s], ph, abort_flag) && mbar_wait(&ctl.b_full[s], ph, abort_flag);
+            for (int kb = 0; kb < nkb && ok; ++kb, ++kc) {
+                const int sa = kc % kAS, sb_ = kc % kBS;
+                if (lane == 0) {
+                    TIMED_WAIT(1, mbar_wait(&ctl.a_full[sa], (kc / kAS) & 1u, abort_flag));
+                    if (ok) TIMED_WAIT(2, mbar_wait(&ctl.b_full[sb_], (kc / kBS) & 1u, abort_flag));
+                }
                 ok = __shfl_sync(0xffffffffu, ok, 0);
                 if (!ok) break;
                 tc_fence_after();
                 if (lane == 0) {
-                    const uint32_t a0 = smem_u32(stages + s * kStage), b0 = a0 + 2 * kTile;
+                    const uint32_t a0 = smem_u32(a_stages + sa * kAStage), b0 = smem_u32(b_stages + sb_ * kTile);
 #pragma unroll
                     for (int acc = 0; acc < 2; ++acc)
 #pragma unroll
                         for (int k = 0; k < kBK / 16; ++k)
                             umma_f16(tmem + buf * 256 + acc * 128, umma_desc(a0 + acc * kTile + k * 32), umma_desc(b0 + k * 32), idesc,
                                      (kb | k) ? 1u : 0u);
-                    umma_commit(&ctl.ab_empty[s]);
+                    umma_commit(&ctl.a_empty[sa]);
+                    umma_commit(&ctl.b_empty[sb_]);
                 }
                 __syncwarp();
             }
             if (lane == 0 && ok) umma_commit(&ctl.acc_full[buf]);
             __syncwarp();
         }
+        if (lane == 0)
+            for (int i = 0; i < 3; ++i) atomicAdd(&g_prefill_cycles[MODE * 16 + 3 + i], (unsigned long long)waited[i]);
         tc_fence_before();
-    } else if (warp < 8) {
-        // ---- dequantizers: thread = accumulator tid / 128, row tid % 128 ----
-        const int acc = tid >> 7, r = tid & 127;
+    } else if (warp < kDequantWarps) {
+        // ---- dequantizers: thread = (K block half kbl, accumulator acc, row r): 64 codes of one row per raw stage ----
+        const int r = tid & 127, acc = (tid >> 7) & 1, kbl = tid >> 8;
         const int gpr = a.K / G;
-        constexpr int NG = 128 / G;  // groups per raw stage (128 codes)
-        uint32_t rawc = 0, abc = 0;
+        constexpr int NG = G >= 64 ? 1 : 64 / G;  // groups in a thread's 64 codes
+        uint32_t rawc = 0;
         bool ok = true;
+        long long waited[2] = {0, 0};
+        const long long t_start = clock64();
         for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
             const int32_t *t = a.tiles + 1 + 3 * (w / a.RB);
             const int64_t row = (int64_t)first_row(t[0], w % a.RB, acc) + r;
             const uint16_t *srow = a.scale + row * gpr, *mrow = a.minv + row * gpr;
             for (int kb2 = 0; kb2 < nkb / 2 && ok; ++kb2, ++rawc) {
                 uint32_t s2[NG], m2[NG];
+                const int g0 = (kb2 * 128 + kbl * 64) / G;
 #pragma unroll
-                for (int g = 0; g < NG; ++g) s2[g] = bf16_to_h2(__ldg(srow + kb2 * NG + g)), m2[g] = bf16_to_h2(__ldg(mrow + kb2 * NG + g));
+                for (int g = 0; g < NG; ++g) s2[g] = bf16_to_h2(__ldg(srow + g0 + g)), m2[g] = bf16_to_h2(__ldg(mrow + g0 + g));
                 const int rs = rawc % kRS;
-                ok = mbar_wait(&ctl.raw_full[rs], (rawc / kRS) & 1u, abort_flag);
+                TIMED_WAIT(0, mbar_wait(&ctl.raw_full[rs], (rawc / kRS) & 1u, abort_flag));
                 if (!ok) break;
                 const uint8_t *rt = raws + rs * kRawStage + acc * kRawTile + r * 64;
-                uint4 c[4];
+                uint4 c[2];
 #pragma unroll
-                for (int j = 0; j < 4; ++j) c[j] = *reinterpret_cast<const uint4 *>(rt + ((j ^ ((r >> 1) & 3)) << 4));
+                for (int j = 0; j < 2; ++j) c[j] = *reinterpret_cast<const uint4 *>(rt + (((kbl * 2 + j) ^ ((r >> 1) & 3)) << 4));
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&ctl.raw_empty[rs]);  // the codes are in registers
+                const uint32_t kc = rawc * 2 + kbl;  // the K block this thread feeds
+                const int s = kc % kAS;
+                TIMED_WAIT(1, mbar_wait(&ctl.a_empty[s], ((kc / kAS) & 1u) ^ 1u, abort_flag));
+                if (!ok) break;
+                uint8_t *ta = a_stages + s * kAStage + acc * kTile;
 #pragma unroll
-                for (int kbl = 0; kbl < 2; ++kbl, ++abc) {
-                    const int s = abc % kS;
-                    ok = mbar_wait(&ctl.ab_empty[s], ((abc / kS) & 1u) ^ 1u, abort_flag);
-                    if (!ok) break;
-                    uint8_t *ta = stages + s * kStage + acc * kTile;
-#pragma unroll
-                    for (int u = 0; u < 8; ++u) {
-                        const uint4 q = c[kbl * 2 + (u >> 2)];
-                        const uint32_t wv = (u & 3) == 0 ? q.x : (u & 3) == 1 ? q.y : (u & 3) == 2 ? q.z : q.w;
-                        const int g = (kbl * 64 + u * 8) / G;
-                        st_chunk(ta, r, u, dequant_word4(wv, s2[g], m2[g]));
-                    }
-                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&ctl.a_full[s]);
+                for (int u = 0; u < 8; ++u) {
+                    const uint4 q = c[u >> 2];
+                    const uint32_t wv = (u & 3) == 0 ? q.x : (u & 3) == 1 ? q.y : (u & 3) == 2 ? q.z : q.w;
+                    const int g = NG == 1 ? 0 : (u * 8) / G;
+                    st_chunk(ta, r, u, dequant_word4(wv, s2[g], m2[g]));
                 }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&ctl.a_full[s]);
             }
         }
+        if (tid == 0) {
+            atomicAdd(&g_prefill_cycles[MODE * 16 + 6], (unsigned long long)waited[0]);
+            atomicAdd(&g_prefill_cycles[MODE * 16 + 7], (unsigned long long)waited[1]);
+            atomicAdd(&g_prefill_cycles[MODE * 16 + 8], (unsigned long long)(clock64() - t_start));
+        }
     } else {
-        // ---- epilogue: warps 8..11, lane quadrant q = warp - 8 ----
-        const int q = warp - 8, r = q * 32 + lane;
+        // ---- epilogue: 8 warps; lane quadrant q = warp % 4, the two warps of a quadrant take alternate 16-column chunks ----
+        const int ew = warp - kDequantWarps, q = ew & 3, half = ew >> 2, r = q * 32 + lane;
         const RouteTables rtab = route_tables(a.ws, a.ws[1], a.ws[2]);
         uint32_t it = 0;
         bool ok = true;
+        long long waited[1] = {0};
+        const long long t_start = clock64();
         for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x, ++it) {
             const int32_t *t = a.tiles + 1 + 3 * (w / a.RB);
             const int rb = w % a.RB, start = t[1], n_valid = t[2];
             const uint32_t buf = it & 1u;
-            ok = mbar_wait(&ctl.acc_full[buf], (it >> 1) & 1u, abort_flag);
+            TIMED_WAIT(0, mbar_wait(&ctl.acc_full[buf], (it >> 1) & 1u, abort_flag));
             if (!ok) break;
             tc_fence_after();
             const uint32_t tbase = tmem + ((uint32_t)(q * 32) << 16) + buf * 256;
-            for (int c0 = 0; c0 < n_valid; c0 += 32) {
-                uint32_t v0[32], v1[32];
-                tmem_ld32(tbase + c0, v0);
-                tmem_ld32(tbase + 128 + c0, v1);
+            for (int c0 = half * 16; c0 < n_valid; c0 += 32) {
+                uint32_t v0[16], v1[16];
+                tmem_ld16(tbase + c0, v0);
+                tmem_ld16(tbase + 128 + c0, v1);
                 tmem_ld_wait();
                 if (MODE == 0) {
                     const int i = rb * kTileM + r;  // intermediate column
                     const int pos = (i & ~7) + ((i & 3) << 1) + ((i >> 2) & 1);
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
+                    for (int j = 0; j < 16; ++j) {
                         if (c0 + j < n_valid) {
                             const float h = swiglu_rounded(__uint_as_float(v0[j]), __uint_as_float(v1[j]), a.bf16_act != 0);
                             a.hs[(int64_t)(start + c0 + j) * a.I + pos] = __half_as_ushort(__float2half_rn(h));
@@ -285,7 +324,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                 } else {
                     const int n = rb * 2 * kTileM + r;
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
+                    for (int j = 0; j < 16; ++j) {
                         if (c0 + j < n_valid) {
                             float *dst = a.partial + (int64_t)rtab.slots[start + c0 + j] * a.N + n;
                             dst[0] = __uint_as_float(v0[j]);
@@ -298,10 +337,16 @@ __global__ void __launch_bounds__(kThreads, 1)
             __syncwarp();
             if (lane == 0) mbar_arrive(&ctl.acc_empty[buf]);
         }
+        if (tid == kDequantWarps * 32) {
+            atomicAdd(&g_prefill_cycles[MODE * 16 + 9], (unsigned long long)waited[0]);
+            atomicAdd(&g_prefill_cycles[MODE * 16 + 10], (unsigned long long)(clock64() - t_start));
+            atomicAdd(&g_prefill_cycles[MODE * 16 + 11], (unsigned long long)it);
+        }
     }
     __syncthreads();
+    if (tid == 0) atomicAdd(&g_prefill_cycles[MODE * 16], (unsigned long long)(clock64() - t_kernel));
     if (tid == 0 && ctl.abort_flag) atomicAdd(&g_prefill_aborts, 1u);
-    if (warp == 13) {
+    if (warp == kMmaWarp) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
     }
@@ -425,7 +470,7 @@ int make_map(const char *fn, CUtensorMap *m, CUtensorMapDataType dt, int es, con
     return 0;
 }
 
-constexpr size_t kFfnSmem = (size_t)kS * kStage + (size_t)kRS * kRawStage + sizeof(Ctl) + 1024;
+constexpr size_t kFfnSmem = (size_t)kAS * kAStage + (size_t)kBS * kTile + (size_t)kRS * kRawStage + sizeof(Ctl) + 1024;
 constexpr size_t kDenseSmem = (size_t)kDS * 2 * kTile + sizeof(DenseCtl) + 1024;
 
 template <int MODE>
@@ -542,6 +587,14 @@ int prefill_experts(PrefillPlan *p, const void *x, int act, const int32_t *ws, i
     a.hs = nullptr, a.partial = partial, a.N = (int)p->d;
     SB_TRY(launch_ffn<1>(fn, p->G_dn, p->dn_raw, p->hs_map, a, p->sms, st));
     return 0;
+}
+
+void prefill_cycles(unsigned long long *out, bool reset) {
+    cudaMemcpyFromSymbol(out, g_prefill_cycles, sizeof(unsigned long long) * 32);
+    if (reset) {
+        unsigned long long z[32] = {};
+        cudaMemcpyToSymbol(g_prefill_cycles, z, sizeof(z));
+    }
 }
 
 unsigned int prefill_aborts() {

@@ -21,6 +21,8 @@ int prefill_router_logits(PrefillPlan *p, const void *x, int64_t M, float *logit
 int prefill_experts(PrefillPlan *p, const void *x, int act, const int32_t *ws, int64_t M, float *partial, cudaStream_t st);
 // CTAs of these kernels that gave up on a bounded wait since the library was loaded.
 unsigned int prefill_aborts();
+// Wait-cycle counters of the FFN kernels' roles, 2 x 16 words (diagnostics; see prefill_umma.cu). Synchronizes.
+void prefill_cycles(unsigned long long *out, bool reset);
 
 // y[m, :] = sum_a coef[m, a] * partial[m * A + a, :] in ascending a; NaN rows for tokens with an invalid id (grouped.cu).
 int combine_reduce(const char *fn, const float *partial, const int32_t *ids, const float *coef, int64_t M, int64_t A, int64_t E, int64_t N,

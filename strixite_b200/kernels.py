@@ -420,6 +420,13 @@ def umma_abort_count():
     return int(lib.strix_umma_abort_count())
 
 
+def umma_wait_cycles(reset=True):
+    """2 x 16 wait-cycle counters of the many-token tensor-core kernels' warp roles (diagnostics)."""
+    out = (C.c_ulonglong * 32)()
+    lib.strix_umma_wait_cycles(out, 1 if reset else 0)
+    return np.array(list(out), dtype=np.uint64).reshape(2, 16)
+
+
 FIXED_PARTIAL_FLOATS = 1 << 20  # STRIX_FIXED_PARTIAL_FLOATS
 
 
