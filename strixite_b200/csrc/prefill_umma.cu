@@ -44,8 +44,8 @@ using namespace sb::umma;
 
 __device__ unsigned int g_prefill_aborts = 0;
 // Cycles the roles of the FFN kernels spent in their waits, summed over CTAs since the last reset (diagnostics):
-// [mode * 16 + i], i = 0 kernel total, 1 producer raw_empty, 2 producer ab_empty, 3 mma acc_empty, 4 mma a_full, 5 mma b_full,
-// 6 dequant raw_full, 7 dequant ab_empty, 8 dequant total, 9 epilogue acc_full, 10 epilogue total, 11 work items.
+// [mode * 16 + i], i = 0 kernel total, 1 producer raw_empty, 2 producer consumed, 3 mma acc_empty, 4 mma full, 5 unused,
+// 6 dequant raw_full, 7 dequant consumed, 8 dequant total, 9 epilogue acc_full, 10 epilogue total, 11 work items.
 __device__ unsigned long long g_prefill_cycles[32];
 
 #define TIMED_WAIT(slot, expr)                 \
@@ -55,21 +55,24 @@ __device__ unsigned long long g_prefill_cycles[32];
         waited[slot] += clock64() - t0_;       \
     } while (0)
 
-constexpr int kBK = 64;                 // K per operand stage: 64 F16 = one 128-byte swizzle row
-constexpr int kTile = kTileM * kBK * 2;  // 16 KB: 128 rows x 64 F16
-constexpr int kAS = 3;                  // A stages: [A0 | A1], two accumulators' weight tiles of one K block
-constexpr int kAStage = 2 * kTile;
-constexpr int kBS = 4;                  // B stages: the token tile of one K block
-constexpr int kRS = 3;                  // raw stages: 2 x (128 rows x 64 bytes) = 128 codes of 256 rows
+constexpr int kBK = 64;                 // K per stage: 64 F16 = one 128-byte swizzle row
+constexpr int kTile = kTileM * kBK * 2;  // 16 KB: 128 rows x 64 F16 (the dense projection's operand tiles)
+constexpr int kTileSlots = 96;          // routed slots per tile = MMA N at most
+constexpr int kBTile = kTileSlots * kBK * 2;  // 12 KB: the token tile of one K block
+constexpr int kBS = 6;                  // token-tile stages
+constexpr int kRS = 6;                  // raw stages: 2 x (128 rows x 64 bytes) = 128 codes of 256 rows
 constexpr int kRawTile = kTileM * 64;
 constexpr int kRawStage = 2 * kRawTile;
+constexpr int kAS = 2;                  // A stages in tensor memory: 2 accumulators x 32 columns (64 F16 per row) each
+// tensor-memory columns: two accumulator buffers of 2 x 96 FP32 columns, then the A stages
+constexpr int kAccCols = kTileSlots, kBufCols = 2 * kAccCols, kAColBase = 2 * kBufCols, kAStageCols = 64;
+static_assert(kAColBase + kAS * kAStageCols <= 512, "tensor memory has 512 columns");
 constexpr int kDequantWarps = 16, kEpilogueWarps = 8;
 constexpr int kProducerWarp = kDequantWarps + kEpilogueWarps, kMmaWarp = kProducerWarp + 1;
 constexpr int kThreads = (kMmaWarp + 1) * 32;
-constexpr int kTileSlots = 128;
 
 struct Ctl {
-    uint64_t raw_full[kRS], raw_empty[kRS], a_full[kAS], a_empty[kAS], b_full[kBS], b_empty[kBS], acc_full[2], acc_empty[2];
+    uint64_t raw_full[kRS], raw_empty[kRS], full[kBS], consumed[kBS], acc_full[2], acc_empty[2];
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -139,14 +142,15 @@ __global__ void __launch_bounds__(kThreads, 1)
     ffn_umma_kernel(const __grid_constant__ CUtensorMap raw_map, const __grid_constant__ CUtensorMap b_map, const FfnArgs a) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t *base = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-    uint8_t *a_stages = base, *b_stages = base + kAS * kAStage, *raws = b_stages + kBS * kTile;
+    uint8_t *b_stages = base, *raws = b_stages + kBS * kBTile;
     Ctl &ctl = *reinterpret_cast<Ctl *>(raws + kRS * kRawStage);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const long long t_kernel = clock64();
     if (tid == 0) {
         for (int i = 0; i < kRS; ++i) mbar_init(&ctl.raw_full[i], 1), mbar_init(&ctl.raw_empty[i], kDequantWarps);
-        for (int i = 0; i < kAS; ++i) mbar_init(&ctl.a_full[i], kDequantWarps / 2), mbar_init(&ctl.a_empty[i], 1);
-        for (int i = 0; i < kBS; ++i) mbar_init(&ctl.b_full[i], 1), mbar_init(&ctl.b_empty[i], 1);
+        // full[kc % kBS]: K block kc is ready = its token tile has landed (the producer's arrival + bytes) and the 8 dequantizer
+        // warps of its half have stored the A stage
+        for (int i = 0; i < kBS; ++i) mbar_init(&ctl.full[i], 1 + kDequantWarps / 2), mbar_init(&ctl.consumed[i], 1);
         for (int i = 0; i < 2; ++i) mbar_init(&ctl.acc_full[i], 1), mbar_init(&ctl.acc_empty[i], kEpilogueWarps);
         ctl.abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -189,10 +193,10 @@ __global__ void __launch_bounds__(kThreads, 1)
                         ++rawc;
                     }
                     const int s = bc % kBS;
-                    TIMED_WAIT(1, mbar_wait(&ctl.b_empty[s], ((bc / kBS) & 1u) ^ 1u, abort_flag));
+                    TIMED_WAIT(1, mbar_wait(&ctl.consumed[s], ((bc / kBS) & 1u) ^ 1u, abort_flag));  // K block bc - kBS is done
                     if (!ok) break;
-                    mbar_expect_tx(&ctl.b_full[s], kTile);
-                    tma_load_2d(b_stages + s * kTile, &b_map, kb * kBK, start, &ctl.b_full[s]);
+                    mbar_expect_tx(&ctl.full[s], kBTile);
+                    tma_load_2d(b_stages + s * kBTile, &b_map, kb * kBK, start, &ctl.full[s]);
                     ++bc;
                 }
             }
@@ -215,23 +219,19 @@ __global__ void __launch_bounds__(kThreads, 1)
             tc_fence_after();
             for (int kb = 0; kb < nkb && ok; ++kb, ++kc) {
                 const int sa = kc % kAS, sb_ = kc % kBS;
-                if (lane == 0) {
-                    TIMED_WAIT(1, mbar_wait(&ctl.a_full[sa], (kc / kAS) & 1u, abort_flag));
-                    if (ok) TIMED_WAIT(2, mbar_wait(&ctl.b_full[sb_], (kc / kBS) & 1u, abort_flag));
-                }
+                if (lane == 0) TIMED_WAIT(1, mbar_wait(&ctl.full[sb_], (kc / kBS) & 1u, abort_flag));
                 ok = __shfl_sync(0xffffffffu, ok, 0);
                 if (!ok) break;
                 tc_fence_after();
                 if (lane == 0) {
-                    const uint32_t a0 = smem_u32(a_stages + sa * kAStage), b0 = smem_u32(b_stages + sb_ * kTile);
+                    const uint32_t a0 = tmem + kAColBase + sa * kAStageCols, b0 = smem_u32(b_stages + sb_ * kBTile);
 #pragma unroll
-                    for (int acc = 0; acc < 2; ++acc)
+                    for (int k = 0; k < kBK / 16; ++k)  // 16 K elements = 8 packed columns of A, 32 bytes of a B row
 #pragma unroll
-                        for (int k = 0; k < kBK / 16; ++k)
-                            umma_f16(tmem + buf * 256 + acc * 128, umma_desc(a0 + acc * kTile + k * 32), umma_desc(b0 + k * 32), idesc,
-                                     (kb | k) ? 1u : 0u);
-                    umma_commit(&ctl.a_empty[sa]);
-                    umma_commit(&ctl.b_empty[sb_]);
+                        for (int acc = 0; acc < 2; ++acc)
+                            umma_f16_ts(tmem + buf * kBufCols + acc * kAccCols, a0 + acc * 32 + k * 8, umma_desc(b0 + k * 32), idesc,
+                                        (kb | k) ? 1u : 0u);
+                    umma_commit(&ctl.consumed[sb_]);  // one commit per K block: it frees this token stage and the A stage
                 }
                 __syncwarp();
             }
@@ -268,21 +268,28 @@ __global__ void __launch_bounds__(kThreads, 1)
                 for (int j = 0; j < 2; ++j) c[j] = *reinterpret_cast<const uint4 *>(rt + (((kbl * 2 + j) ^ ((r >> 1) & 3)) << 4));
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&ctl.raw_empty[rs]);  // the codes are in registers
-                const uint32_t kc = rawc * 2 + kbl;  // the K block this thread feeds
-                const int s = kc % kAS;
-                TIMED_WAIT(1, mbar_wait(&ctl.a_empty[s], ((kc / kAS) & 1u) ^ 1u, abort_flag));
-                if (!ok) break;
-                uint8_t *ta = a_stages + s * kAStage + acc * kTile;
+                uint32_t av[32];  // 64 F16 of this row: tensor-memory columns 0..31 of the stage's accumulator half
 #pragma unroll
                 for (int u = 0; u < 8; ++u) {
                     const uint4 q = c[u >> 2];
                     const uint32_t wv = (u & 3) == 0 ? q.x : (u & 3) == 1 ? q.y : (u & 3) == 2 ? q.z : q.w;
                     const int g = NG == 1 ? 0 : (u * 8) / G;
-                    st_chunk(ta, r, u, dequant_word4(wv, s2[g], m2[g]));
+                    const uint4 o = dequant_word4(wv, s2[g], m2[g]);
+                    av[4 * u] = o.x, av[4 * u + 1] = o.y, av[4 * u + 2] = o.z, av[4 * u + 3] = o.w;
                 }
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                // converted first: only the store into tensor memory waits for the stage
+                const uint32_t kc = rawc * 2 + kbl;  // the K block this thread feeds
+                const int s = kc % kAS;
+                if (kc >= kAS) {  // the stage is free once K block kc - kAS has been consumed
+                    const uint32_t pc = kc - kAS;
+                    TIMED_WAIT(1, mbar_wait(&ctl.consumed[pc % kBS], (pc / kBS) & 1u, abort_flag));
+                    if (!ok) break;
+                }
+                tmem_st32(tmem + ((uint32_t)(r & ~31) << 16) + kAColBase + s * kAStageCols + acc * 32, av);
+                tmem_st_wait();
+                tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&ctl.a_full[s]);
+                if (lane == 0) mbar_arrive(&ctl.full[kc % kBS]);
             }
         }
         if (tid == 0) {
@@ -305,11 +312,11 @@ __global__ void __launch_bounds__(kThreads, 1)
             TIMED_WAIT(0, mbar_wait(&ctl.acc_full[buf], (it >> 1) & 1u, abort_flag));
             if (!ok) break;
             tc_fence_after();
-            const uint32_t tbase = tmem + ((uint32_t)(q * 32) << 16) + buf * 256;
+            const uint32_t tbase = tmem + ((uint32_t)(q * 32) << 16) + buf * kBufCols;
             for (int c0 = half * 16; c0 < n_valid; c0 += 32) {
                 uint32_t v0[16], v1[16];
                 tmem_ld16(tbase + c0, v0);
-                tmem_ld16(tbase + 128 + c0, v1);
+                tmem_ld16(tbase + kAccCols + c0, v1);
                 tmem_ld_wait();
                 if (MODE == 0) {
                     const int i = rb * kTileM + r;  // intermediate column
@@ -455,22 +462,22 @@ int encoder(const char *fn, EncodeFn *out) {
     return 0;
 }
 
-// rows x cols elements of `es` bytes, row pitch = cols * es, box = 128 rows x box_cols.
+// rows x cols elements of `es` bytes, row pitch = cols * es, box = box_rows x box_cols.
 int make_map(const char *fn, CUtensorMap *m, CUtensorMapDataType dt, int es, const void *ptr, int64_t rows, int64_t cols, int box_cols,
-             CUtensorMapSwizzle sw) {
+             CUtensorMapSwizzle sw, int box_rows = 128) {
     EncodeFn enc;
     SB_TRY(encoder(fn, &enc));
     SB_CHECK(reinterpret_cast<uintptr_t>(ptr) % 16 == 0 && (cols * es) % 16 == 0, fn, ": tensor ", ptr, " with a row pitch of ", cols * es,
              " bytes is not 16-byte aligned");
     const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows}, strides[1] = {(cuuint64_t)(cols * es)};
-    const cuuint32_t box[2] = {(cuuint32_t)box_cols, 128}, estr[2] = {1, 1};
+    const cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows}, estr[2] = {1, 1};
     const CUresult rc = enc(m, dt, 2, const_cast<void *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
                             CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     SB_CHECK(rc == CUDA_SUCCESS, fn, ": cuTensorMapEncodeTiled failed with ", (int)rc, " for a [", rows, ", ", cols, "] tensor");
     return 0;
 }
 
-constexpr size_t kFfnSmem = (size_t)kAS * kAStage + (size_t)kBS * kTile + (size_t)kRS * kRawStage + sizeof(Ctl) + 1024;
+constexpr size_t kFfnSmem = (size_t)kBS * kBTile + (size_t)kRS * kRawStage + sizeof(Ctl) + 1024;
 constexpr size_t kDenseSmem = (size_t)kDS * 2 * kTile + sizeof(DenseCtl) + 1024;
 
 template <int MODE>
@@ -530,8 +537,8 @@ int prefill_create(const strix_moe_layer_desc &d, int64_t A, int64_t Estack, int
     alloc(reinterpret_cast<void **>(&p->tiles), (size_t)(1 + 3 * (S / kTileSlots + Estack + 2)) * 4);
     if (rc == 0) rc = make_map(fn, &p->gu_raw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, d.gate_up.q, Estack * 2 * d.I, d.d / 2, 64, CU_TENSOR_MAP_SWIZZLE_64B);
     if (rc == 0) rc = make_map(fn, &p->dn_raw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, d.down.q, Estack * d.d, d.I / 2, 64, CU_TENSOR_MAP_SWIZZLE_64B);
-    if (rc == 0) rc = make_map(fn, &p->xg_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, p->xg, S, d.d, kBK, CU_TENSOR_MAP_SWIZZLE_128B);
-    if (rc == 0) rc = make_map(fn, &p->hs_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, p->hs, S, d.I, kBK, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc == 0) rc = make_map(fn, &p->xg_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, p->xg, S, d.d, kBK, CU_TENSOR_MAP_SWIZZLE_128B, kTileSlots);
+    if (rc == 0) rc = make_map(fn, &p->hs_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, p->hs, S, d.I, kBK, CU_TENSOR_MAP_SWIZZLE_128B, kTileSlots);
     p->dense_router = d.act == kBF16 && d.router_kind == STRIX_ROUTER_BF16 && d.d % kBK == 0;
     if (rc == 0 && p->dense_router)
         rc = make_map(fn, &p->rw_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, d.router_w, router_rows, d.d, kBK, CU_TENSOR_MAP_SWIZZLE_128B);
