@@ -252,12 +252,13 @@ int strix_moe_layer_forward(strix_moe_layer *L, const void *x, int64_t M, void *
     }
     // 1. Router logits, FP32 [M, R]; row E (when gated) is the shared expert's gate.
     const bool tensor_path = L->prefill != nullptr && M >= kPrefillMinTokens;
-    if (tensor_path && sb::prefill_has_dense_router(L->prefill)) SB_TRY(sb::prefill_router_logits(L->prefill, x, M, L->logits, st));
+    const bool dense_router = tensor_path && sb::prefill_has_dense_router(L->prefill);
+    if (dense_router) SB_TRY(sb::prefill_router_logits(L->prefill, x, M, L->logits, d.router_bias, E, st));  // bias added in its epilogue
     else if (d.router_kind == STRIX_ROUTER_Q) SB_TRY(linear_any(d.router_bits, x, &d.router_q, L->logits, M, act, STRIX_ACT_F32, stream));
     else if (d.router_kind == STRIX_ROUTER_BF16)
         SB_TRY(strix_linear_bf16w(x, static_cast<const uint16_t *>(d.router_w), L->logits, M, R, d.d, act, STRIX_ACT_F32, stream));
     else SB_TRY(strix_linear_f32w(x, static_cast<const float *>(d.router_w), L->logits, M, R, d.d, act, STRIX_ACT_F32, stream));
-    if (d.router_bias != nullptr) {
+    if (d.router_bias != nullptr && !dense_router) {
         add_bias_kernel<<<(unsigned)((M * E + 255) / 256), 256, 0, st>>>(L->logits, R, M, E, d.router_bias);
         SB_LAUNCH_OK(fn, ": router bias");
     }

@@ -369,7 +369,8 @@ struct DenseCtl {
 };
 
 __global__ void __launch_bounds__(192, 1)
-    dense_umma_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap x_map, int K, int R, int M, float *logits) {
+    dense_umma_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap x_map, int K, int R, int M, float *logits,
+                      const float *bias, int n_bias) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t *stages = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     DenseCtl &ctl = *reinterpret_cast<DenseCtl *>(stages + kDS * 2 * kTile);
@@ -424,13 +425,14 @@ __global__ void __launch_bounds__(192, 1)
         if (mbar_wait(&ctl.acc_full, 0, abort_flag)) {
             tc_fence_after();
             const int r = r0 + warp * 32 + lane;
+            const float b = bias != nullptr && r < n_bias ? bias[r] : 0.f;  // the same FP32 add a separate pass would do
             for (int c0 = 0; c0 < 128 && m0 + c0 < M; c0 += 32) {
                 uint32_t v[32];
                 tmem_ld32(tmem + ((uint32_t)(warp * 32) << 16) + c0, v);
                 tmem_ld_wait();
 #pragma unroll
                 for (int j = 0; j < 32; ++j)
-                    if (r < R && m0 + c0 + j < M) logits[(int64_t)(m0 + c0 + j) * R + r] = __uint_as_float(v[j]);
+                    if (r < R && m0 + c0 + j < M) logits[(int64_t)(m0 + c0 + j) * R + r] = __uint_as_float(v[j]) + b;
             }
         }
         tc_fence_before();
@@ -560,7 +562,7 @@ void prefill_destroy(PrefillPlan *p) {
 
 bool prefill_has_dense_router(const PrefillPlan *p) { return p->dense_router; }
 
-int prefill_router_logits(PrefillPlan *p, const void *x, int64_t M, float *logits, cudaStream_t st) {
+int prefill_router_logits(PrefillPlan *p, const void *x, int64_t M, float *logits, const float *bias, int64_t n_bias, cudaStream_t st) {
     const char *fn = "moe_layer_forward (tensor-core router)";
     CUtensorMap xm;
     SB_TRY(make_map(fn, &xm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, M, p->d, kBK, CU_TENSOR_MAP_SWIZZLE_128B));
@@ -572,7 +574,7 @@ int prefill_router_logits(PrefillPlan *p, const void *x, int64_t M, float *logit
         prepared = dev;
     }
     const dim3 grid((unsigned)((p->router_rows + kTileM - 1) / kTileM), (unsigned)((M + 127) / 128));
-    dense_umma_kernel<<<grid, 192, kDenseSmem, st>>>(p->rw_map, xm, (int)p->d, (int)p->router_rows, (int)M, logits);
+    dense_umma_kernel<<<grid, 192, kDenseSmem, st>>>(p->rw_map, xm, (int)p->d, (int)p->router_rows, (int)M, logits, bias, (int)n_bias);
     SB_LAUNCH_OK(fn, " M=", M, " R=", p->router_rows, " K=", p->d);
     return 0;
 }

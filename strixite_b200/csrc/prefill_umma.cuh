@@ -15,7 +15,8 @@ int prefill_create(const strix_moe_layer_desc &d, int64_t A, int64_t Estack, int
 void prefill_destroy(PrefillPlan *p);
 // BF16 activations with a BF16 router: the router projection runs on the tensor cores too.
 bool prefill_has_dense_router(const PrefillPlan *p);
-int prefill_router_logits(PrefillPlan *p, const void *x, int64_t M, float *logits, cudaStream_t st);
+// bias (optional, n_bias entries) is added to rows r < n_bias.
+int prefill_router_logits(PrefillPlan *p, const void *x, int64_t M, float *logits, const float *bias, int64_t n_bias, cudaStream_t st);
 // Tiles -> bucket-ordered F16 activations -> gate/up + SwiGLU -> down: FP32 partial[slot, d] for every slot with a
 // valid expert. `ws` is the grouping workspace of moe_group_routes for (M, A, Estack).
 int prefill_experts(PrefillPlan *p, const void *x, int act, const int32_t *ws, int64_t M, float *partial, cudaStream_t st);
