@@ -279,7 +279,7 @@ int strix_moe_layer_forward(strix_moe_layer *L, const void *x, int64_t M, void *
         // many tokens on the tensor cores: bucket-ordered F16 activations, gate/up with SwiGLU in its epilogue, down into
         // FP32 partials, then the ordered reduction of the reference's combine
         SB_TRY(strix_moe_group_routes(L->ids, M, A, L->Estack, L->group_ws, L->group_ws_bytes, expert_err, stream));
-        SB_TRY(sb::prefill_experts(L->prefill, x, act, static_cast<const int32_t *>(L->group_ws), M, L->partial, st));
+        SB_TRY(sb::prefill_experts(L->prefill, x, act, static_cast<const int32_t *>(L->group_ws), M, A, L->partial, st));
         SB_TRY(sb::combine_reduce(fn, L->partial, L->ids, L->coef, M, A, L->Estack, d.d, y, act, st));
     } else if (M >= d.grouped_min_tokens) {
         SB_TRY(strix_moe_group_routes(L->ids, M, A, L->Estack, L->group_ws, L->group_ws_bytes, expert_err, stream));
@@ -313,6 +313,27 @@ int strix_moe_layer_forward(strix_moe_layer *L, const void *x, int64_t M, void *
         else SB_TRY(strix_residual_add(y, L->sh_y, M * d.d, act, stream));
     }
     return 0;
+}
+
+int strix_moe_layer_experts_partial(strix_moe_layer *L, const void *rows, const int32_t *ids, int64_t n, float *partial, void *stream) {
+    const char *fn = "moe_layer_experts_partial";
+    SB_CHECK(L != nullptr && rows != nullptr && ids != nullptr && partial != nullptr, fn, ": null pointer");
+    SB_CHECK(L->prefill != nullptr, fn, ": the layer has no tensor-core plan (needs math != F32, uniform 4-bit stacks, d % 256 == 0, I % 128 == 0 and max_tokens >= ",
+             kPrefillMinTokens, ")");
+    SB_CHECK(n >= 1 && n <= L->d.max_tokens * L->A, fn, ": ", n, " rows, expected 1..", L->d.max_tokens * L->A);
+    auto st = static_cast<cudaStream_t>(stream);
+    SB_TRY(strix_moe_group_routes(ids, n, 1, L->Estack, L->group_ws, L->group_ws_bytes, L->err + 3, stream));
+    SB_TRY(sb::prefill_experts(L->prefill, rows, L->d.act, static_cast<const int32_t *>(L->group_ws), n, 1, partial, st));
+    return 0;
+}
+
+int strix_moe_combine_reduce(const float *partial, const int32_t *ids, const float *coef, int64_t M, int64_t A, int64_t E, int64_t N, void *y,
+                             int act, void *stream) {
+    const char *fn = "moe_combine_reduce";
+    SB_CHECK(partial != nullptr && ids != nullptr && coef != nullptr && y != nullptr, fn, ": null pointer");
+    SB_CHECK(M >= 1 && A >= 1 && A <= 64 && N >= 1 && E >= 1 && M * A <= (1 << 20), fn, ": M = ", M, ", A = ", A, ", N = ", N, ", E = ", E);
+    SB_CHECK(act_ok(act), fn, ": unsupported activation dtype ", act);
+    return sb::combine_reduce(fn, partial, ids, coef, M, A, E, N, y, act, static_cast<cudaStream_t>(stream));
 }
 
 int strix_moe_layer_forward_host(strix_moe_layer *L, const void *x_host, int64_t M, void *y_host, void *stream) {

@@ -3,6 +3,7 @@
 // contiguous 512-byte run; up to 8 activation rows share each weight pass; a shuffle reduction ends the row.
 // FP32 accumulation; the output is rounded once (BF16) or stored as accumulated (F32).
 #include "common.cuh"
+#include "prefill_umma.cuh"
 
 #include "strixite_b200.h"
 
@@ -180,6 +181,11 @@ int strix_linear_q8(const void *x, const strix_qview *w, void *y, int64_t M, int
 }
 int strix_linear_bf16w(const void *x, const uint16_t *w, void *y, int64_t M, int64_t N, int64_t K, int act,
                        int out_act, void *stream) {
+    // many BF16 tokens with FP32 outputs (the router projection of a prefill chunk): the tensor-core kernel. Products of two
+    // BF16 values are exact in FP32, so only the summation order differs from the FMA kernel.
+    if (x != nullptr && w != nullptr && y != nullptr && act == STRIX_ACT_BF16 && out_act == STRIX_ACT_F32 && N >= 1 &&
+        sb::dense_bf16_ok(x, w, M, N, K) && reinterpret_cast<uintptr_t>(y) % 4 == 0)
+        return sb::dense_bf16("linear_bf16w", x, w, static_cast<float *>(y), M, N, K, nullptr, 0, static_cast<cudaStream_t>(stream));
     return linear_w<uint16_t>("linear_bf16w", x, w, y, M, N, K, act, out_act, stream);
 }
 int strix_linear_f32w(const void *x, const float *w, void *y, int64_t M, int64_t N, int64_t K, int act, int out_act,

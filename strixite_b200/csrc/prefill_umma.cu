@@ -579,13 +579,37 @@ int prefill_router_logits(PrefillPlan *p, const void *x, int64_t M, float *logit
     return 0;
 }
 
-int prefill_experts(PrefillPlan *p, const void *x, int act, const int32_t *ws, int64_t M, float *partial, cudaStream_t st) {
+int dense_bf16(const char *fn, const void *x, const uint16_t *w, float *y, int64_t M, int64_t N, int64_t K, const float *bias, int64_t n_bias,
+               cudaStream_t st) {
+    CUtensorMap xm, wm;
+    SB_TRY(make_map(fn, &xm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, M, K, kBK, CU_TENSOR_MAP_SWIZZLE_128B));
+    SB_TRY(make_map(fn, &wm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, w, N, K, kBK, CU_TENSOR_MAP_SWIZZLE_128B));
+    static thread_local int prepared = -1;
+    int dev = 0;
+    SB_CUDA(cudaGetDevice(&dev), fn);
+    if (prepared != dev) {
+        SB_CUDA(cudaFuncSetAttribute(dense_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kDenseSmem), fn);
+        prepared = dev;
+    }
+    const dim3 grid((unsigned)((N + kTileM - 1) / kTileM), (unsigned)((M + 127) / 128));
+    dense_umma_kernel<<<grid, 192, kDenseSmem, st>>>(wm, xm, (int)K, (int)N, (int)M, y, bias, (int)n_bias);
+    SB_LAUNCH_OK(fn, " (tensor cores) M=", M, " N=", N, " K=", K);
+    return 0;
+}
+
+bool dense_bf16_ok(const void *x, const void *w, int64_t M, int64_t N, int64_t K) {
+    return M >= 64 && K % kBK == 0 && K <= (1 << 24) && N <= (1 << 24) && M <= (1 << 24) && reinterpret_cast<uintptr_t>(x) % 16 == 0 &&
+           reinterpret_cast<uintptr_t>(w) % 16 == 0;
+}
+
+int prefill_experts(PrefillPlan *p, const void *x, int act, const int32_t *ws, int64_t M, int64_t A, float *partial, cudaStream_t st) {
     const char *fn = "moe_layer_forward (tensor-core experts)";
     tiles_kernel<<<1, 1024, 0, st>>>(ws, p->tiles);
     SB_LAUNCH_OK(fn, ": tiles");
-    const unsigned gblocks = (unsigned)std::min<int64_t>((M * p->A + 7) / 8, 148 * 16);
-    if (act == kF32) pregather_kernel<float><<<gblocks, 256, 0, st>>>((const float *)x, ws, p->A, p->d, p->xg);
-    else pregather_kernel<uint16_t><<<gblocks, 256, 0, st>>>((const uint16_t *)x, ws, p->A, p->d, p->xg);
+    SB_CHECK(M * A <= p->max_tokens * p->A, fn, ": ", M * A, " slots exceed the layer's ", p->max_tokens * p->A);
+    const unsigned gblocks = (unsigned)std::min<int64_t>((M * A + 7) / 8, 148 * 16);
+    if (act == kF32) pregather_kernel<float><<<gblocks, 256, 0, st>>>((const float *)x, ws, A, p->d, p->xg);
+    else pregather_kernel<uint16_t><<<gblocks, 256, 0, st>>>((const uint16_t *)x, ws, A, p->d, p->xg);
     SB_LAUNCH_OK(fn, ": gather");
     FfnArgs a{};
     a.ws = ws, a.tiles = p->tiles;

@@ -415,6 +415,12 @@ def linear_q4_experts_combine_grouped(h, w, E, ids, coef, ws, ws_bytes, partial,
     _combine_grouped(4, h, w, E, ids, coef, ws, ws_bytes, partial, M, A, y, act, math, stream)
 
 
+def moe_combine_reduce(partial, ids, coef, M, A, E, N, y, act, stream=None):
+    """y[m, :] = sum_a coef[m, a] * partial[m * A + a, :], a ascending, one rounding (the second half of
+    strixite kernels/moe_grouped.hpp:60-62 linear_q4_experts_combine_grouped)."""
+    call("strix_moe_combine_reduce", _p(partial), _p(ids), _p(coef), M, A, E, N, _p(y), int(act), _s(stream))
+
+
 def umma_abort_count():
     """Thread blocks of the tensor-core kernels that abandoned a bounded wait since the library was loaded (0 when healthy)."""
     return int(lib.strix_umma_abort_count())
