@@ -6,6 +6,8 @@ roofline of the dominant kernel and the CPU baseline timed beside it.
 One "step" = one pass of the MoE layer over one batch of synthetic tokens. Workloads (the benchmark configurations):
   decode1      1 token,  d 2048, I 512, 512 experts top-10 + shared (stacked, gated), q4 G128, FP32 router      [config 1]
   verify6      6 tokens, same shapes, experts q4, router and shared expert (separate) q8 G64                   [config 2]
+  ep_prefill16384  16384 BF16 tokens over all ranks, Zipf(1.1) router bias, the 512 experts sharded over the ranks (expert parallel:
+               all-to-all dispatch and combine), strong scaling                                                  [config 5]
   prefill4096  4096 BF16 tokens, per-expert router bias N(0, 0.5), q4 experts, shared stacked                 [config 3]
   stack4       4 layers d 4096, I 1024, 6 tokens, per-expert q4/q5/q6/q8 60/15/15/10 %, residual adds          [config 4]
 Weights are seeded N(0, 0.02) packed by the library's device quantizer; activations N(0, 1); there are no
@@ -34,6 +36,8 @@ WORKLOADS = {
     "decode1": dict(M=1, d=2048, I=512, E=512, k=10, act="f32", router="f32", shared="stacked", mix=None, bias=None, ring=24, layers=1),
     "verify6": dict(M=6, d=2048, I=512, E=512, k=10, act="f32", router="q8", shared="separate", mix=None, bias=None, ring=16, layers=1),
     "prefill4096": dict(M=4096, d=2048, I=512, E=512, k=10, act="bf16", router="bf16", shared="stacked", mix=None, bias=0.5, ring=2, layers=1, math=2),
+    "ep_prefill16384": dict(M=16384, d=2048, I=512, E=512, k=10, act="bf16", router="bf16", shared="stacked", mix=None, bias="zipf", ring=2, layers=1,
+                            math=2, ep=True),
     "stack4": dict(M=6, d=4096, I=1024, E=512, k=10, act="f32", router="f32", shared="stacked", mix=[0.6, 0.15, 0.15, 0.1], bias=None, ring=2,
                    layers=4),
 }
@@ -190,7 +194,7 @@ def build_ring(cfg, rank, device):
                 bias = (np.random.default_rng(seed + 7).standard_normal(cfg["E"]) * cfg["bias"]).astype(np.float32)
             layers.append(synth.make_layer(seed, cfg["d"], cfg["I"], cfg["E"], cfg["k"], act, G=G_EXPERTS, router=cfg["router"], shared=cfg["shared"],
                                            mix=cfg["mix"], bias=bias, max_tokens=cfg["M"], grouped_min_tokens=cfg.get("grouped_min", 6),
-                                           math=cfg.get("math", 0), device=device))
+                                           math=cfg.get("math", 0), decode_impl=cfg.get("decode_impl", 0), device=device))
         g.manual_seed(7000 + 100 * rank + r)
         x = torch.randn((cfg["M"], cfg["d"]), generator=g, device=device, dtype=torch.float32)
         x = x if cfg["act"] == "f32" else x.to(torch.bfloat16)
@@ -312,6 +316,97 @@ def cpu_baseline(ring, cfg, budget_s=12.0, max_tokens=None):
                 sample="%d passes of %d token(s) through ring entry 0 (%d layer(s)), %.1f s" % (n, M, len(Ls), dt)), one
 
 
+def run_ep(args, cfg, rank, world, local, device, dist, barrier, line, P):
+    """Config 5: one layer, its routed experts sharded over the ranks, the token batch split evenly (strong scaling)."""
+    import torch
+
+    from strixite_b200 import ep as EP
+    from strixite_b200 import kernels as K
+    from strixite_b200 import synth
+
+    if dist is None:  # one rank: the same code path over a one-rank group
+        import torch.distributed as dist
+
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29533")
+        dist.init_process_group("nccl", rank=0, world_size=1, device_id=torch.device(device))
+        barrier = lambda: None  # noqa: E731
+    d, I, E, k, T = cfg["d"], cfg["I"], cfg["E"], cfg["k"], cfg["M"]
+    Tl = T // world
+    g = torch.Generator(device=device)
+    g.manual_seed(4242)
+    rw = (torch.randn((E + 1, d), generator=g, device=device, dtype=torch.float32) * 0.02).to(torch.bfloat16)  # replicated: same seed everywhere
+    bias = torch.from_numpy(synth.zipf_bias(99, E)).to(device)
+    gu = synth.quantized_normal(501, 4, (E + 1) * 2 * I, d, G_EXPERTS, device=device)
+    dn = synth.quantized_normal(502, 4, (E + 1) * d, I, G_EXPERTS, device=device)
+    gu_l, dn_l = EP.shard_stack(gu, E, world, rank), EP.shard_stack(dn, E, world, rank)
+    del gu, dn
+    torch.cuda.empty_cache()
+    # capacity: with Zipf routing the hot rank receives several times the mean; 3x the mean plus the shared slots, checked below
+    cap = min(T * (k + 1), 3 * T * k // world + Tl + 4096)
+    layer = EP.cuda_layer(d, I, E, k, K.Act.BF16, rw, bias, gu_l, dn_l, world, rank, max_local_tokens=Tl, capacity=cap)
+    xs = []
+    for r in range(cfg["ring"]):
+        g.manual_seed(9000 + 17 * r)
+        xs.append(torch.randn((T, d), generator=g, device=device, dtype=torch.float32)[rank * Tl:(rank + 1) * Tl].to(torch.bfloat16).contiguous())
+    for i in range(max(3, args.warmup)):
+        y = layer.forward(xs[i % len(xs)])
+    torch.cuda.synchronize()
+    barrier()
+    sampler = ClockSampler(local)
+    sampler.start()
+    torch.cuda.cudart().cudaProfilerStart()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    recv = []
+    for i in range(args.steps):
+        y = layer.forward(xs[i % len(xs)])
+        recv.append(sum(layer.last["received"]))
+    e1.record()
+    torch.cuda.synchronize()
+    torch.cuda.cudart().cudaProfilerStop()
+    barrier()
+    clocks = sampler.stop()
+    ms = e0.elapsed_time(e1)
+    stats = torch.tensor([ms, float(np.mean(recv))], device=device)
+    mx = stats.clone()
+    dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+    sm = stats.clone()
+    dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+    ms = float(mx[0].item())
+    # end to end: host tokens in, host outputs back, every step
+    xh = [x.cpu().pin_memory() for x in xs]
+    yh = torch.empty_like(xh[0]).pin_memory()
+    ke = max(3, args.steps // 4)
+    barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for i in range(ke):
+        xd = xh[i % len(xh)].to(device, non_blocking=True)
+        yh.copy_(layer.forward(xd), non_blocking=True)
+        torch.cuda.synchronize()
+    dt = torch.tensor([time.perf_counter() - t0], device=device)
+    dist.all_reduce(dt, op=dist.ReduceOp.MAX)
+    fl = 2.0 * T * (k + 1) * 3 * I * d + 2.0 * T * (E + 1) * d
+    step_s = ms * 1e-3 / args.steps
+    line["scaling"] = "strong"
+    line["config"].update(parallelism="expert parallel x%d (experts e -> rank e / %d, tokens split evenly, shared expert replicated)" % (world, E // world),
+                          router_bias="Zipf(1.1)", tokens_per_step=T, l2="two token sets alternate; every step streams far more than the 126 MB L2")
+    line.update(value=T / step_s, ms_per_step=ms / args.steps, clocks=clocks)
+    line["e2e"] = dict(value=T * ke / float(dt.item()), unit="tokens/s", h2d_bytes_per_step=int(xh[0].numel() * 2 * world), d2h_bytes_per_step=int(yh.numel() * 2 * world),
+                       steps=ke, note="pinned host tokens -> device -> expert-parallel layer -> pinned host outputs, per rank, wall clock, max over ranks")
+    ach = fl / step_s / 1e12
+    line["roofline"] = dict(bound="tensor", achieved=ach, peak=P["tensor"] * world, unit="TFLOP/s", frac=ach / (P["tensor"] * world), traffic=None,
+                            peak_source=P["source"], algorithmic_flops_per_step=fl, kernel="whole step, all ranks",
+                            load_imbalance_max_over_mean_slots=float(mx[1].item() / (sm[1].item() / world)))
+    line["gpu_launches"] = None
+    line["gpu_launches_note"] = "per step and rank: 2 router kernels, grouping, tiles, gather, 2 tcgen05 FFN kernels, reduce, plus torch index kernels and 4 NCCL collectives"
+    if rank == 0:
+        print(json.dumps(line))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -320,8 +415,10 @@ def main():
     ap.add_argument("--workload", default="verify6", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--decode-impl", type=int, default=0, choices=[0, 1], help="forwards of <= 8 tokens: 0 = the fused kernel, 1 = the per-function kernels")
     args = ap.parse_args()
     cfg = dict(WORKLOADS[args.workload])
+    cfg["decode_impl"] = args.decode_impl
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local = int(os.environ.get("LOCAL_RANK", 0))
     if args.warmup < 3:
@@ -370,6 +467,9 @@ def main():
         print(json.dumps(line))
         return
 
+    if cfg.get("ep"):
+        run_ep(args, cfg, rank, world, local, device, dist, barrier, line, P)
+        return
     ring = build_ring(cfg, rank, device)
     n = len(ring)
     for e in ring:  # warm every entry once outside any capture (first-call set-up, lazy module loads)

@@ -266,9 +266,11 @@ int strix_moe_stack_forward(strix_moe_layer *const *layers, int64_t n_layers, vo
 int strix_moe_layer_experts_partial(strix_moe_layer *layer, const void *rows, const int32_t *ids, int64_t n, float *partial,
                                     void *stream);
 /* The ordered weighted sum of the reference's combine (kernels/moe_grouped.hpp:60-62, second half): y[m, :] = sum over a
- * ascending of coef[m, a] * partial[m * A + a, :], one rounding; a token with an id outside [0, E) gets a NaN row. */
-int strix_moe_combine_reduce(const float *partial, const int32_t *ids, const float *coef, int64_t M, int64_t A, int64_t E,
-                             int64_t N, void *y, int act, void *stream);
+ * ascending of coef[m, a] * partial[m * A + a, :], one rounding; a token with an id outside [0, E) gets a NaN row.
+ * pos (optional, [M * A]): slot (m, a) is row pos[m * A + a] of partial instead of row m * A + a - partial rows that
+ * came back from other devices in another order are summed where they lie. */
+int strix_moe_combine_reduce(const float *partial, const int64_t *pos, const int32_t *ids, const float *coef, int64_t M,
+                             int64_t A, int64_t E, int64_t N, void *y, int act, void *stream);
 /* Device pointer of a named intermediate of the last forward - the reference's probes (runtime/qwen4exp.hpp:179-188):
  * "router_logits" f32 [M, E(+1)], "router_ids" i32 [M, A], "router_coef" f32 [M, A], "experts_h" [M, A, I],
  * "shared_h" [M, I], "shared_y" [M, d], "err" u32 [6] (router words 0..2, expert words 3..5), "group_ws". */

@@ -82,7 +82,7 @@ SIGNATURES = {
     "strix_linear_q4_experts_combine_grouped_fixed": [_vp, _qv, _i64, _vp, _vp, _vp, _sz, _i64, _i64, _vp, _int, _int, _vp],
     "strix_linear_qmix_experts_gather_grouped": [_vp, _qm, _vp, _sz, _i64, _i64, _vp, _int, _int, _vp],
     "strix_linear_qmix_experts_combine_grouped": [_vp, _qm, _vp, _vp, _vp, _sz, _vp, _i64, _i64, _vp, _int, _int, _vp],
-    "strix_moe_combine_reduce": [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _int, _vp],
+    "strix_moe_combine_reduce": [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _int, _vp],
     "strix_umma_abort_count": [],
     "strix_umma_wait_cycles": [_vp, _int],
     "strix_last_error": [],

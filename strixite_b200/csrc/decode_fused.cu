@@ -263,6 +263,12 @@ __device__ __forceinline__ bool grid_wait(const uint32_t *counter, uint32_t *abo
     return sm.abort_flag == 0;
 }
 
+// The FP32 copy of x in shared memory keeps each 32-value chunk's eight 16-byte pieces XOR-rotated by the chunk index, so
+// that lanes reading the same piece of 32 consecutive chunks (the quantized router rows: one chunk per lane) spread over
+// all banks instead of colliding on four. Only with a quantized router: the unquantized rows read consecutive pieces per
+// lane and keep the plain layout. k: a multiple of 4.
+__device__ __forceinline__ int xf_index(int k) { return (k & ~31) + ((((k >> 2) ^ (k >> 5)) & 7) << 2); }
+
 // ---- phase 1: router logits ----------------------------------------------------------------------------------------
 // Two warps per router row (each half of K), all M tokens at once; x as FP32 from shared memory. The halves meet in
 // shared memory after a block barrier.
@@ -284,11 +290,10 @@ __device__ __forceinline__ void router_half_row(const DecodeParams &p, const flo
 #pragma unroll
                 for (int m = 0; m < kMaxTok; ++m) {
                     if (m < M) {
-                        const float4 *xv = reinterpret_cast<const float4 *>(xf + m * K + c * 32);
                         float dot = 0.f, xs = 0.f;
 #pragma unroll
                         for (int i = 0; i < 8; ++i) {
-                            const float4 f = xv[i];
+                            const float4 f = *reinterpret_cast<const float4 *>(xf + m * K + xf_index(c * 32 + 4 * i));
                             dot = fmaf(f.x, code[4 * i], dot), dot = fmaf(f.y, code[4 * i + 1], dot);
                             dot = fmaf(f.z, code[4 * i + 2], dot), dot = fmaf(f.w, code[4 * i + 3], dot);
                             xs += (f.x + f.y) + (f.z + f.w);
@@ -553,7 +558,21 @@ __device__ __forceinline__ void dn_issue(const DecodeParams &p, const Group &grp
     }
 }
 
-template <typename T>
+// by_bits over the formats a kernel variant was compiled for (bit 0: 4 bits, 1: 5, 2: 6, 3: 8): the variants for uniform
+// 4-bit experts carry a quarter of the code of the general one, which the instruction cache rewards.
+template <int FMASK, typename F>
+__device__ __forceinline__ void by_bits_in(int bits, F &&f) {
+    if constexpr (FMASK == 0x1) {
+        f(std::integral_constant<int, 4>{});
+    } else if constexpr (FMASK == 0x9) {
+        if (bits == 4) f(std::integral_constant<int, 4>{});
+        else f(std::integral_constant<int, 8>{});
+    } else {
+        by_bits(bits, f);
+    }
+}
+
+template <typename T, int FMASK>
 __global__ void __launch_bounds__(kThreads, 1) decode_fused_kernel(const __grid_constant__ DecodeParams p) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     Smem &sm = *reinterpret_cast<Smem *>(smem_raw);
@@ -605,8 +624,9 @@ __global__ void __launch_bounds__(kThreads, 1) decode_fused_kernel(const __grid_
             s_hi += bf16_bits_to_f32(hi[j]), s_lo += bf16_bits_to_f32(lo[j]);
         }
         if (valid) {
-            float4 *dst = reinterpret_cast<float4 *>(xf + m * d + u * 8);
-            dst[0] = make_float4(v[0], v[1], v[2], v[3]), dst[1] = make_float4(v[4], v[5], v[6], v[7]);
+            const bool rot = p.router_kind == STRIX_ROUTER_Q;
+            *reinterpret_cast<float4 *>(xf + m * d + (rot ? xf_index(u * 8) : u * 8)) = make_float4(v[0], v[1], v[2], v[3]);
+            *reinterpret_cast<float4 *>(xf + m * d + (rot ? xf_index(u * 8 + 4) : u * 8 + 4)) = make_float4(v[4], v[5], v[6], v[7]);
             uint4 h4;
             h4.x = hi[0] | ((uint32_t)hi[4] << 16), h4.y = hi[1] | ((uint32_t)hi[5] << 16), h4.z = hi[2] | ((uint32_t)hi[6] << 16), h4.w = hi[3] | ((uint32_t)hi[7] << 16);
             *reinterpret_cast<uint4 *>(xp + m * tok_stride + u * 16) = h4;
@@ -735,7 +755,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_fused_kernel(const __grid_
                             if (ps < np && tk < M) xsp[ps][e] = xsum + (tk * planes + pl) * xs_row + (G == 32 ? 0 : G == 64 ? nchunk_x : nchunk_x + nchunk_x / 2) + h * gl;
                         }
                     }
-                    by_bits(grp.bits[0], [&](auto bc) {
+                    by_bits_in<FMASK>(grp.bits[0], [&](auto bc) {
                         constexpr int BITS = decltype(bc)::value;
                         for (int qg = 0; qg < gl; ++qg) {
                             float xs[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
@@ -914,7 +934,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_fused_kernel(const __grid_
                             }
                         }
                     }
-                    by_bits(grp.bits[1], [&](auto bc) {
+                    by_bits_in<FMASK>(grp.bits[1], [&](auto bc) {
                         constexpr int BITS = decltype(bc)::value;
                         for (int qg = 0; qg < gpr; ++qg) {
                             float xs[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
@@ -1073,10 +1093,15 @@ int decode_fused_plan(DecodeParams &p, int max_bits_gate_up, int max_bits_down, 
 int decode_fused_launch(const char *fn, const DecodeParams &p, cudaStream_t stream) {
     int dev = 0;
     SB_CUDA(cudaGetDevice(&dev), fn);
+    // expert formats present (the plan's fmask) pick the smallest kernel variant that covers them
+    const int variant = (p.fmask & ~0x1) == 0 ? 0 : (p.fmask & ~0x9) == 0 ? 1 : 2;
+    using KernelFn = void (*)(const DecodeParams);
+    static const KernelFn kernels[2][3] = {{decode_fused_kernel<float, 0x1>, decode_fused_kernel<float, 0x9>, decode_fused_kernel<float, 0xF>},
+                                           {decode_fused_kernel<uint16_t, 0x1>, decode_fused_kernel<uint16_t, 0x9>, decode_fused_kernel<uint16_t, 0xF>}};
     static thread_local int prepared_dev = -1;
     if (prepared_dev != dev) {
-        SB_CUDA(cudaFuncSetAttribute(decode_fused_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, p.smem_bytes), fn);
-        SB_CUDA(cudaFuncSetAttribute(decode_fused_kernel<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, p.smem_bytes), fn);
+        for (int a = 0; a < 2; ++a)
+            for (int v = 0; v < 3; ++v) SB_CUDA(cudaFuncSetAttribute(kernels[a][v], cudaFuncAttributeMaxDynamicSharedMemorySize, p.smem_bytes), fn);
         prepared_dev = dev;
     }
     const int grid = sm_count();
@@ -1086,8 +1111,7 @@ int decode_fused_launch(const char *fn, const DecodeParams &p, cudaStream_t stre
     attr[0].id = cudaLaunchAttributeCooperative;
     attr[0].val.cooperative = 1;
     cfg.attrs = attr, cfg.numAttrs = 1;
-    if (p.act == kF32) SB_CUDA(cudaLaunchKernelEx(&cfg, decode_fused_kernel<float>, p), fn, ": launching the fused decode kernel");
-    else SB_CUDA(cudaLaunchKernelEx(&cfg, decode_fused_kernel<uint16_t>, p), fn, ": launching the fused decode kernel");
+    SB_CUDA(cudaLaunchKernelEx(&cfg, kernels[p.act == kF32 ? 0 : 1][variant], p), fn, ": launching the fused decode kernel");
     return 0;
 }
 

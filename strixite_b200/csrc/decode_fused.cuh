@@ -30,6 +30,7 @@ struct DecodeParams {
     uint32_t *sync;  // 16 words, zero before the first launch: two barrier counters, CTAs done, abort; [8..15] phase timestamps
     // shared-memory plan, computed on the host (decode_fused_plan)
     int smem_bytes;
+    int fmask;  // expert formats present (bit 0: 4 bits, 1: 5, 2: 6, 3: 8), set by the caller: selects the kernel variant
     int gu_nk;  // K slices (= warps) per gate/up tile
     int gu_row_stride, gu_scale_bytes, gu_stage_bytes, gu_stages;
     int gu_active, gu_depth;  // consumer warps in use and stages per warp (gu_stages = gu_active * gu_depth)

@@ -218,12 +218,25 @@ __global__ void __launch_bounds__(256)
 // The same on four consecutive outputs per thread: 16-byte loads of the partial rows, four of them in flight per step.
 template <typename T>
 __global__ void __launch_bounds__(256)
-    combine_reduce4_kernel(const float *partial, const int32_t *ids, const float *coef, int64_t M, int64_t A, int64_t E, int64_t N, T *y) {
+    combine_reduce4_kernel(const float *partial, const int64_t *pos, const int32_t *ids, const float *coef, int64_t M, int64_t A, int64_t E,
+                           int64_t N, T *y) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, N4 = N / 4;
     if (i >= M * N4) return;
     const int64_t m = i / N4, n = (i - m * N4) * 4;
     bool ok = true;
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (pos != nullptr) {  // slot (m, a) lives in row pos[m * A + a] of partial
+        for (int64_t a = 0; a < A; ++a) {
+            const float4 p = __ldcs(reinterpret_cast<const float4 *>(partial + pos[m * A + a] * N + n));
+            const float c = coef[m * A + a];
+            const int32_t id = ids[m * A + a];
+            ok = ok && id >= 0 && id < E;
+            v.x = fmaf(c, p.x, v.x), v.y = fmaf(c, p.y, v.y), v.z = fmaf(c, p.z, v.z), v.w = fmaf(c, p.w, v.w);
+        }
+        const float q = qnan();
+        st_act(y, m * N + n, ok ? v.x : q), st_act(y, m * N + n + 1, ok ? v.y : q), st_act(y, m * N + n + 2, ok ? v.z : q), st_act(y, m * N + n + 3, ok ? v.w : q);
+        return;
+    }
     const float *row = partial + m * A * N + n;
     int64_t a = 0;
     for (; a + 4 <= A; a += 4) {
@@ -342,11 +355,13 @@ int combine_grouped(const char *fn, const void *h, const StackView &w, int64_t E
 }
 
 int combine_reduce(const char *fn, const float *partial, const int32_t *ids, const float *coef, int64_t M, int64_t A, int64_t E, int64_t N,
-                   void *y, int act, cudaStream_t st) {
-    if (N % 4 == 0 && reinterpret_cast<uintptr_t>(partial) % 16 == 0 && reinterpret_cast<uintptr_t>(y) % 16 == 0) {
+                   void *y, int act, cudaStream_t st, const int64_t *pos) {
+    const bool vec = N % 4 == 0 && reinterpret_cast<uintptr_t>(partial) % 16 == 0 && reinterpret_cast<uintptr_t>(y) % 16 == 0;
+    SB_CHECK(pos == nullptr || vec, fn, ": the indexed combine needs N % 4 == 0 and 16-byte aligned buffers");
+    if (vec) {
         const unsigned blocks = (unsigned)((M * (N / 4) + 255) / 256);
-        if (act == kF32) combine_reduce4_kernel<float><<<blocks, 256, 0, st>>>(partial, ids, coef, M, A, E, N, (float *)y);
-        else combine_reduce4_kernel<uint16_t><<<blocks, 256, 0, st>>>(partial, ids, coef, M, A, E, N, (uint16_t *)y);
+        if (act == kF32) combine_reduce4_kernel<float><<<blocks, 256, 0, st>>>(partial, pos, ids, coef, M, A, E, N, (float *)y);
+        else combine_reduce4_kernel<uint16_t><<<blocks, 256, 0, st>>>(partial, pos, ids, coef, M, A, E, N, (uint16_t *)y);
     } else {
         const unsigned blocks = (unsigned)((M * N + 255) / 256);
         if (act == kF32) combine_reduce_kernel<float><<<blocks, 256, 0, st>>>(partial, ids, coef, M, A, E, N, (float *)y);

@@ -11,7 +11,7 @@
 //              tcgen05.mma reads. Global loads of block kb + 1 are in flight while block kb is converted.
 //   warp 4     allocates 128 tensor-memory columns, then one elected lane issues tcgen05.mma (cta_group::1, kind::f16,
 //              F16 x F16 -> FP32 in tensor memory) for each K block as its stage fills, and releases the stage with
-//              tcgen05.commit. No cluster, no multicast.
+//              tcgen05.commit. One CTA per tile, no cluster.
 //   epilogue   tcgen05.ld 32 lanes x 32 columns per warp: lane = weight row, column = token, so for each token the 32
 //              lanes store 32 consecutive output values (coalesced) to y[slot, n0 + row] or partial[slot, n0 + row].
 //

@@ -180,6 +180,10 @@ int strix_moe_layer_create(const strix_moe_layer_desc *desc, strix_moe_layer **o
             minG = d.sh_gate_up.G < minG ? d.sh_gate_up.G : minG, minG = d.sh_down.G < minG ? d.sh_down.G : minG;
             al(d.sh_gate_up.scale), al(d.sh_gate_up.minv), al(d.sh_down.scale), al(d.sh_down.minv), al(d.sh_gate_up.q), al(d.sh_down.q);
         }
+        // the expert formats the kernel will meet (bit 0: 4 bits, 1: 5, 2: 6, 3: 8): picks the kernel variant
+        auto fbit = [](int bits) { return bits == 4 ? 1 : bits == 5 ? 2 : bits == 6 ? 4 : 8; };
+        p.fmask = d.experts_mixed ? 0xF : (fbit(d.gate_up_bits) | fbit(d.down_bits));
+        if (d.shared_mode == STRIX_SHARED_SEPARATE) p.fmask |= fbit(d.sh_gate_up_bits) | fbit(d.sh_down_bits);
         L->fused_ok = rc == 0 && aligned && d.decode_impl == 0 && sb::decode_fused_plan(p, bits_gu, bits_dn, (int)minG) != 0;
         if (L->fused_ok) {
             a(dev_alloc(&L->hrec, (size_t)((Mf * L->A + Mf) * p.hrec_bytes), "fused decode h records"));
@@ -327,13 +331,13 @@ int strix_moe_layer_experts_partial(strix_moe_layer *L, const void *rows, const 
     return 0;
 }
 
-int strix_moe_combine_reduce(const float *partial, const int32_t *ids, const float *coef, int64_t M, int64_t A, int64_t E, int64_t N, void *y,
-                             int act, void *stream) {
+int strix_moe_combine_reduce(const float *partial, const int64_t *pos, const int32_t *ids, const float *coef, int64_t M, int64_t A, int64_t E,
+                             int64_t N, void *y, int act, void *stream) {
     const char *fn = "moe_combine_reduce";
     SB_CHECK(partial != nullptr && ids != nullptr && coef != nullptr && y != nullptr, fn, ": null pointer");
     SB_CHECK(M >= 1 && A >= 1 && A <= 64 && N >= 1 && E >= 1 && M * A <= (1 << 20), fn, ": M = ", M, ", A = ", A, ", N = ", N, ", E = ", E);
     SB_CHECK(act_ok(act), fn, ": unsupported activation dtype ", act);
-    return sb::combine_reduce(fn, partial, ids, coef, M, A, E, N, y, act, static_cast<cudaStream_t>(stream));
+    return sb::combine_reduce(fn, partial, ids, coef, M, A, E, N, y, act, static_cast<cudaStream_t>(stream), pos);
 }
 
 int strix_moe_layer_forward_host(strix_moe_layer *L, const void *x_host, int64_t M, void *y_host, void *stream) {

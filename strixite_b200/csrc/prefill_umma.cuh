@@ -33,6 +33,6 @@ void prefill_cycles(unsigned long long *out, bool reset);
 
 // y[m, :] = sum_a coef[m, a] * partial[m * A + a, :] in ascending a; NaN rows for tokens with an invalid id (grouped.cu).
 int combine_reduce(const char *fn, const float *partial, const int32_t *ids, const float *coef, int64_t M, int64_t A, int64_t E, int64_t N,
-                   void *y, int act, cudaStream_t st);
+                   void *y, int act, cudaStream_t st, const int64_t *pos = nullptr);  // pos: slot (m, a) is row pos[m * A + a] of partial
 
 }  // namespace sb

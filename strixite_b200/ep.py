@@ -27,7 +27,7 @@ class ExpertParallelMoe:
     def __init__(self, E, k, world, rank, route_fn, experts_fn, reduce_fn, group=None, shared=True):
         """E routed experts (E % world == 0), top-k; `shared`: a stacked shared expert with id E rides slot k.
         route_fn(x) -> (ids int32 [T, A], coef float32 [T, A]);  experts_fn(rows [n, d], local_ids int32 [n]) -> float32 [n, d];
-        reduce_fn(partial float32 [T * A, d], ids, coef) -> y [T, d]."""
+        reduce_fn(partial float32 [T * A, d], pos int64 [T * A], ids, coef) -> y [T, d], slot (t, a) being row pos[t * A + a]."""
         if E % world != 0:
             raise ValueError("ExpertParallelMoe: %d experts do not divide over %d ranks" % (E, world))
         self.E, self.k, self.world, self.rank, self.group = E, k, world, rank, group
@@ -49,27 +49,50 @@ class ExpertParallelMoe:
         counts = torch.bincount(dest, minlength=self.world)
         return order, local[order].to(torch.int32), counts
 
-    def forward(self, x):
+    def forward(self, x, timings=None):
+        """y [T, d] for this rank's tokens x [T, d]. timings: an optional dict that receives the milliseconds of each phase
+        (CUDA events; adds a synchronization at the end)."""
         T, d = x.shape
+        marks = []
+
+        def mark(name):
+            if timings is not None and x.is_cuda:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record()
+                marks.append((name, ev))
+
+        mark("start")
         ids, coef = self.route_fn(x)
+        mark("route")
         order, send_ids, counts = self.plan(ids)
         send_rows = x.index_select(0, torch.div(order, self.A, rounding_mode="floor"))
+        mark("plan+gather")
         # counts both ways (host integers: all_to_all_single wants split sizes)
         recv_counts = torch.empty_like(counts)
         dist.all_to_all_single(recv_counts, counts, group=self.group)
         out_splits, in_splits = counts.tolist(), recv_counts.tolist()
+        mark("counts")
         n_recv = int(sum(in_splits))
         recv_rows = x.new_empty((n_recv, d))
         recv_ids = send_ids.new_empty((n_recv,))
         dist.all_to_all_single(recv_rows, send_rows, in_splits, out_splits, group=self.group)
         dist.all_to_all_single(recv_ids, send_ids, in_splits, out_splits, group=self.group)
+        mark("dispatch")
         partial = self.experts_fn(recv_rows, recv_ids) if n_recv else torch.empty((0, d), dtype=torch.float32, device=x.device)
+        mark("experts")
         back = torch.empty((T * self.A, d), dtype=torch.float32, device=x.device)
         dist.all_to_all_single(back, partial, out_splits, in_splits, group=self.group)
-        home = torch.empty_like(back)
-        home.index_copy_(0, order, back)  # back to slot order t * A + a
+        mark("combine all-to-all")
+        pos = torch.empty_like(order)
+        pos[order] = torch.arange(order.numel(), device=order.device)  # slot t * A + a came back as row pos[t * A + a]
         self.last = dict(ids=ids, coef=coef, sent=out_splits, received=in_splits)
-        return self.reduce_fn(home, ids, coef)
+        y = self.reduce_fn(back, pos, ids, coef)
+        mark("reduce")
+        if marks:
+            torch.cuda.synchronize()
+            for (_, a), (name, b) in zip(marks[:-1], marks[1:]):
+                timings[name] = timings.get(name, 0.0) + a.elapsed_time(b)
+        return y
 
 
 def cuda_layer(d, I, E, k, act, router_w, router_bias, gate_up_local, down_local, world, rank, max_local_tokens, capacity=None, group=None,
@@ -106,10 +129,10 @@ def cuda_layer(d, I, E, k, act, router_w, router_bias, gate_up_local, down_local
     def experts(rows, local_ids):
         return shard.experts_partial(rows, local_ids)
 
-    def reduce(partial, ids, coef):
+    def reduce(partial, pos, ids, coef):
         T = ids.shape[0]
         y = torch.empty((T, d), dtype=K._dtype(act), device=partial.device)
-        K.moe_combine_reduce(partial, ids, coef, T, A, E + 1, d, y, act)
+        K.moe_combine_reduce(partial, ids, coef, T, A, E + 1, d, y, act, pos=pos)
         return y
 
     ep = ExpertParallelMoe(E, k, world, rank, route, experts, reduce, group=group)

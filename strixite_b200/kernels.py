@@ -415,10 +415,11 @@ def linear_q4_experts_combine_grouped(h, w, E, ids, coef, ws, ws_bytes, partial,
     _combine_grouped(4, h, w, E, ids, coef, ws, ws_bytes, partial, M, A, y, act, math, stream)
 
 
-def moe_combine_reduce(partial, ids, coef, M, A, E, N, y, act, stream=None):
+def moe_combine_reduce(partial, ids, coef, M, A, E, N, y, act, stream=None, pos=None):
     """y[m, :] = sum_a coef[m, a] * partial[m * A + a, :], a ascending, one rounding (the second half of
-    strixite kernels/moe_grouped.hpp:60-62 linear_q4_experts_combine_grouped)."""
-    call("strix_moe_combine_reduce", _p(partial), _p(ids), _p(coef), M, A, E, N, _p(y), int(act), _s(stream))
+    strixite kernels/moe_grouped.hpp:60-62 linear_q4_experts_combine_grouped). pos (int64 [M * A]): the row of partial
+    that holds each slot, when the rows are not in slot order."""
+    call("strix_moe_combine_reduce", _p(partial), None if pos is None else _p(pos), _p(ids), _p(coef), M, A, E, N, _p(y), int(act), _s(stream))
 
 
 def umma_abort_count():

@@ -42,8 +42,8 @@ def _oracle_callables(L, world, rank):
         y, _ = oracle.experts_combine(np.ascontiguousarray(h.reshape(-1, I)), L["down"], gid, np.ones_like(gid, dtype=np.float32))
         return torch.from_numpy(y)
 
-    def reduce(partial, ids, coef):
-        p = partial.numpy().astype(np.float64).reshape(ids.shape[0], ids.shape[1], -1)
+    def reduce(partial, pos, ids, coef):
+        p = partial.numpy()[pos.numpy()].astype(np.float64).reshape(ids.shape[0], ids.shape[1], -1)
         return torch.from_numpy((coef.numpy().astype(np.float64)[:, :, None] * p).sum(axis=1).astype(np.float32))
 
     return route, experts, reduce
