@@ -415,10 +415,13 @@ def main():
     ap.add_argument("--workload", default="verify6", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--ring", type=int, default=0, help="override the number of independent (weights, tokens) pairs cycled (a small ring keeps a profiler capture small)")
     ap.add_argument("--decode-impl", type=int, default=0, choices=[0, 1], help="forwards of <= 8 tokens: 0 = the fused kernel, 1 = the per-function kernels")
     args = ap.parse_args()
     cfg = dict(WORKLOADS[args.workload])
     cfg["decode_impl"] = args.decode_impl
+    if args.ring > 0:
+        cfg["ring"] = args.ring
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local = int(os.environ.get("LOCAL_RANK", 0))
     if args.warmup < 3:

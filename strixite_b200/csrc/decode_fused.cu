@@ -572,7 +572,10 @@ __device__ __forceinline__ void by_bits_in(int bits, F &&f) {
     }
 }
 
-template <typename T, int FMASK>
+// G128: every 4-bit projection has groups of 128 codes (its unrolled group loop is the only one compiled for 4 bits; other
+// formats run the general loop).
+// ONEPASS: the MMA columns hold every token in one pass (BF16 activations, or at most 4 FP32 tokens).
+template <typename T, int FMASK, bool G128, bool ONEPASS>
 __global__ void __launch_bounds__(kThreads, 1) decode_fused_kernel(const __grid_constant__ DecodeParams p) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     Smem &sm = *reinterpret_cast<Smem *>(smem_raw);
@@ -731,7 +734,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_fused_kernel(const __grid_
                 const int t = (int)blockIdx.x + tl * (int)gridDim.x;
                 const int gi = t / tiles_per_group, jb = t - gi * tiles_per_group;
                 const Group &grp = sm.groups[gi];
-                const int np = (planes == 2 && (grp.mask >> 4)) ? 2 : 1;  // token passes
+                const int np = (!ONEPASS && planes == 2 && (grp.mask >> 4)) ? 2 : 1;  // token passes
                 float tot[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
                 {
                     const int G = grp.G[0], gpr = d / G, gl = gpr / nk;  // groups per row, per slice
@@ -765,17 +768,21 @@ __global__ void __launch_bounds__(kThreads, 1) decode_fused_kernel(const __grid_
                                 for (int e = 0; e < 2; ++e)
                                     if (xsp[ps][e]) xs[ps][e] = xsp[ps][e][qg];
                             const float sA = bf16_bits_to_f32(scA[qg]), mA = bf16_bits_to_f32(mnA[qg]), sB = bf16_bits_to_f32(scB[qg]), mB = bf16_bits_to_f32(mnB[qg]);
-                            if (np == 1) {
+                            if (ONEPASS || np == 1) {
                                 const uint8_t *const xb1[1] = {xb[0]};
                                 const float xs1[1][2] = {{xs[0][0], xs[0][1]}};
                                 float t1[1][4] = {{0.f, 0.f, 0.f, 0.f}};
-                                if (G == 128) group_dot<BITS, 1, 4>(rowA, rowB, Ks, xb1, qg * 16, 4, c, sA, mA, sB, mB, xs1, t1);
+                                if constexpr (G128 && BITS == 4) group_dot<BITS, 1, 4>(rowA, rowB, Ks, xb1, qg * 16, 4, c, sA, mA, sB, mB, xs1, t1);
+                                else if constexpr (G128) group_dot<BITS, 1, 0>(rowA, rowB, Ks, xb1, qg * (G / 8), G / 32, c, sA, mA, sB, mB, xs1, t1);
+                                else if (G == 128) group_dot<BITS, 1, 4>(rowA, rowB, Ks, xb1, qg * 16, 4, c, sA, mA, sB, mB, xs1, t1);
                                 else group_dot<BITS, 1, 0>(rowA, rowB, Ks, xb1, qg * (G / 8), G / 32, c, sA, mA, sB, mB, xs1, t1);
 #pragma unroll
                                 for (int i = 0; i < 4; ++i) tot[0][i] += t1[0][i];
-                            } else {
+                            } else if constexpr (!ONEPASS) {
                                 const uint8_t *const xb2[2] = {xb[0], xb[1]};
-                                if (G == 128) group_dot<BITS, 2, 4>(rowA, rowB, Ks, xb2, qg * 16, 4, c, sA, mA, sB, mB, xs, tot);
+                                if constexpr (G128 && BITS == 4) group_dot<BITS, 2, 4>(rowA, rowB, Ks, xb2, qg * 16, 4, c, sA, mA, sB, mB, xs, tot);
+                                else if constexpr (G128) group_dot<BITS, 2, 0>(rowA, rowB, Ks, xb2, qg * (G / 8), G / 32, c, sA, mA, sB, mB, xs, tot);
+                                else if (G == 128) group_dot<BITS, 2, 4>(rowA, rowB, Ks, xb2, qg * 16, 4, c, sA, mA, sB, mB, xs, tot);
                                 else group_dot<BITS, 2, 0>(rowA, rowB, Ks, xb2, qg * (G / 8), G / 32, c, sA, mA, sB, mB, xs, tot);
                             }
                         }
@@ -914,7 +921,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_fused_kernel(const __grid_
                     const uint8_t *st = my_stages + (size_t)slot * stage_bytes;
                     const uint8_t *rowA = st + g * rs, *rowB = st + (g + 8) * rs;
                     const uint16_t *sc = reinterpret_cast<const uint16_t *>(st + sc_off), *mn = reinterpret_cast<const uint16_t *>(st + sc_off + sc_bytes);
-                    const int np = (planes == 2 && (grp.mask >> 4)) ? 2 : 1;
+                    const int np = (!ONEPASS && planes == 2 && (grp.mask >> 4)) ? 2 : 1;
                     const bool is_sh = grp.expert == -2;
                     const uint8_t *xb[2] = {nullptr, nullptr};
                     const float *hp[2][2] = {{nullptr, nullptr}, {nullptr, nullptr}};
@@ -954,17 +961,21 @@ __global__ void __launch_bounds__(kThreads, 1) decode_fused_kernel(const __grid_
                             const float sA = bf16_bits_to_f32(sc[g * gpr + qg]), mA = bf16_bits_to_f32(mn[g * gpr + qg]);
                             const float sB = bf16_bits_to_f32(sc[(g + 8) * gpr + qg]), mB = bf16_bits_to_f32(mn[(g + 8) * gpr + qg]);
                             float v[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-                            if (np == 1) {
+                            if (ONEPASS || np == 1) {
                                 const uint8_t *const xb1[1] = {xb[0]};
                                 const float xs1[1][2] = {{xs[0][0], xs[0][1]}};
                                 float t1[1][4] = {{0.f, 0.f, 0.f, 0.f}};
-                                if (G == 128) group_dot<BITS, 1, 4>(rowA, rowB, I, xb1, qg * 16, 4, c, sA, mA, sB, mB, xs1, t1);
+                                if constexpr (G128 && BITS == 4) group_dot<BITS, 1, 4>(rowA, rowB, I, xb1, qg * 16, 4, c, sA, mA, sB, mB, xs1, t1);
+                                else if constexpr (G128) group_dot<BITS, 1, 0>(rowA, rowB, I, xb1, qg * (G / 8), G / 32, c, sA, mA, sB, mB, xs1, t1);
+                                else if (G == 128) group_dot<BITS, 1, 4>(rowA, rowB, I, xb1, qg * 16, 4, c, sA, mA, sB, mB, xs1, t1);
                                 else group_dot<BITS, 1, 0>(rowA, rowB, I, xb1, qg * (G / 8), G / 32, c, sA, mA, sB, mB, xs1, t1);
 #pragma unroll
                                 for (int i = 0; i < 4; ++i) v[0][i] = t1[0][i];
-                            } else {
+                            } else if constexpr (!ONEPASS) {
                                 const uint8_t *const xb2[2] = {xb[0], xb[1]};
-                                if (G == 128) group_dot<BITS, 2, 4>(rowA, rowB, I, xb2, qg * 16, 4, c, sA, mA, sB, mB, xs, v);
+                                if constexpr (G128 && BITS == 4) group_dot<BITS, 2, 4>(rowA, rowB, I, xb2, qg * 16, 4, c, sA, mA, sB, mB, xs, v);
+                                else if constexpr (G128) group_dot<BITS, 2, 0>(rowA, rowB, I, xb2, qg * (G / 8), G / 32, c, sA, mA, sB, mB, xs, v);
+                                else if (G == 128) group_dot<BITS, 2, 4>(rowA, rowB, I, xb2, qg * 16, 4, c, sA, mA, sB, mB, xs, v);
                                 else group_dot<BITS, 2, 0>(rowA, rowB, I, xb2, qg * (G / 8), G / 32, c, sA, mA, sB, mB, xs, v);
                             }
 #pragma unroll
@@ -1093,15 +1104,21 @@ int decode_fused_plan(DecodeParams &p, int max_bits_gate_up, int max_bits_down, 
 int decode_fused_launch(const char *fn, const DecodeParams &p, cudaStream_t stream) {
     int dev = 0;
     SB_CUDA(cudaGetDevice(&dev), fn);
-    // expert formats present (the plan's fmask) pick the smallest kernel variant that covers them
-    const int variant = (p.fmask & ~0x1) == 0 ? 0 : (p.fmask & ~0x9) == 0 ? 1 : 2;
+    // the expert formats present (fmask), whether every group has 128 codes, and whether one MMA pass covers the tokens pick the
+    // smallest kernel variant that covers the call: a quarter of the general kernel's code for uniform 4-bit G = 128 experts
+    const bool one_pass = p.act != kF32 || p.M <= 4;
+    const int fm = !p.g128_4bit ? 2 : (p.fmask & ~0x1) == 0 ? 0 : (p.fmask & ~0x9) == 0 ? 1 : 2;
+    const int variant = fm == 2 ? 4 : fm * 2 + (one_pass ? 0 : 1);
     using KernelFn = void (*)(const DecodeParams);
-    static const KernelFn kernels[2][3] = {{decode_fused_kernel<float, 0x1>, decode_fused_kernel<float, 0x9>, decode_fused_kernel<float, 0xF>},
-                                           {decode_fused_kernel<uint16_t, 0x1>, decode_fused_kernel<uint16_t, 0x9>, decode_fused_kernel<uint16_t, 0xF>}};
+    static const KernelFn kernels[2][5] = {
+        {decode_fused_kernel<float, 0x1, true, true>, decode_fused_kernel<float, 0x1, true, false>, decode_fused_kernel<float, 0x9, true, true>,
+         decode_fused_kernel<float, 0x9, true, false>, decode_fused_kernel<float, 0xF, false, false>},
+        {decode_fused_kernel<uint16_t, 0x1, true, true>, decode_fused_kernel<uint16_t, 0x1, true, true>, decode_fused_kernel<uint16_t, 0x9, true, true>,
+         decode_fused_kernel<uint16_t, 0x9, true, true>, decode_fused_kernel<uint16_t, 0xF, false, false>}};
     static thread_local int prepared_dev = -1;
     if (prepared_dev != dev) {
         for (int a = 0; a < 2; ++a)
-            for (int v = 0; v < 3; ++v) SB_CUDA(cudaFuncSetAttribute(kernels[a][v], cudaFuncAttributeMaxDynamicSharedMemorySize, p.smem_bytes), fn);
+            for (int v = 0; v < 5; ++v) SB_CUDA(cudaFuncSetAttribute(kernels[a][v], cudaFuncAttributeMaxDynamicSharedMemorySize, p.smem_bytes), fn);
         prepared_dev = dev;
     }
     const int grid = sm_count();

@@ -31,6 +31,7 @@ struct DecodeParams {
     // shared-memory plan, computed on the host (decode_fused_plan)
     int smem_bytes;
     int fmask;  // expert formats present (bit 0: 4 bits, 1: 5, 2: 6, 3: 8), set by the caller: selects the kernel variant
+    int g128_4bit;  // every 4-bit projection (experts, separate shared expert) uses groups of 128 codes, set by the caller
     int gu_nk;  // K slices (= warps) per gate/up tile
     int gu_row_stride, gu_scale_bytes, gu_stage_bytes, gu_stages;
     int gu_active, gu_depth;  // consumer warps in use and stages per warp (gu_stages = gu_active * gu_depth)

@@ -184,6 +184,9 @@ int strix_moe_layer_create(const strix_moe_layer_desc *desc, strix_moe_layer **o
         auto fbit = [](int bits) { return bits == 4 ? 1 : bits == 5 ? 2 : bits == 6 ? 4 : 8; };
         p.fmask = d.experts_mixed ? 0xF : (fbit(d.gate_up_bits) | fbit(d.down_bits));
         if (d.shared_mode == STRIX_SHARED_SEPARATE) p.fmask |= fbit(d.sh_gate_up_bits) | fbit(d.sh_down_bits);
+        p.g128_4bit = !d.experts_mixed && (d.gate_up_bits != 4 || d.gate_up.G == 128) && (d.down_bits != 4 || d.down.G == 128);
+        if (d.shared_mode == STRIX_SHARED_SEPARATE)
+            p.g128_4bit = p.g128_4bit && (d.sh_gate_up_bits != 4 || d.sh_gate_up.G == 128) && (d.sh_down_bits != 4 || d.sh_down.G == 128);
         L->fused_ok = rc == 0 && aligned && d.decode_impl == 0 && sb::decode_fused_plan(p, bits_gu, bits_dn, (int)minG) != 0;
         if (L->fused_ok) {
             a(dev_alloc(&L->hrec, (size_t)((Mf * L->A + Mf) * p.hrec_bytes), "fused decode h records"));
