@@ -18,9 +18,9 @@
 //               "1024 + code", exact subtract, one F16 FMA) stored in the K-major 128-byte-swizzled layout the tensor
 //               core reads (3-deep ring of [A0 | A1]). Both operands keep each 8 K elements in the order
 //               0,4,1,5,2,6,3,7 (what the nibble unpack produces); xg and hs are written in that order.
-//   warp 25     allocates all 512 tensor-memory columns (two buffers of two 128-column accumulators) and issues
-//               tcgen05.mma (cta_group::1, kind::f16, FP32 accumulation); tcgen05.commit frees operand stages and
-//               publishes finished accumulators.
+//   warps 25-26 one per accumulator: issue tcgen05.mma (cta_group::1, kind::f16, FP32 accumulation, A from tensor memory);
+//               tcgen05.commit frees operand stages and publishes finished accumulators. Warp 25 allocates all 512
+//               tensor-memory columns (two buffers of two 96-column accumulators + two A stages of 64 columns).
 //   warps 16-23 epilogue: tcgen05.ld (lane = weight row, column = routed slot) of one buffer while the next work item
 //               accumulates in the other.
 // Every mbarrier wait is bounded: on expiry the CTA raises the abort counter, frees its tensor memory and returns.
@@ -68,8 +68,8 @@ constexpr int kAS = 2;                  // A stages in tensor memory: 2 accumula
 constexpr int kAccCols = kTileSlots, kBufCols = 2 * kAccCols, kAColBase = 2 * kBufCols, kAStageCols = 64;
 static_assert(kAColBase + kAS * kAStageCols <= 512, "tensor memory has 512 columns");
 constexpr int kDequantWarps = 16, kEpilogueWarps = 8;
-constexpr int kProducerWarp = kDequantWarps + kEpilogueWarps, kMmaWarp = kProducerWarp + 1;
-constexpr int kThreads = (kMmaWarp + 1) * 32;
+constexpr int kProducerWarp = kDequantWarps + kEpilogueWarps, kMmaWarp = kProducerWarp + 1;  // warps kMmaWarp and kMmaWarp + 1 issue MMAs
+constexpr int kThreads = (kMmaWarp + 2) * 32;
 
 struct Ctl {
     uint64_t raw_full[kRS], raw_empty[kRS], full[kBS], consumed[kBS], acc_full[2], acc_empty[2];
@@ -150,8 +150,8 @@ __global__ void __launch_bounds__(kThreads, 1)
         for (int i = 0; i < kRS; ++i) mbar_init(&ctl.raw_full[i], 1), mbar_init(&ctl.raw_empty[i], kDequantWarps);
         // full[kc % kBS]: K block kc is ready = its token tile has landed (the producer's arrival + bytes) and the 8 dequantizer
         // warps of its half have stored the A stage
-        for (int i = 0; i < kBS; ++i) mbar_init(&ctl.full[i], 1 + kDequantWarps / 2), mbar_init(&ctl.consumed[i], 1);
-        for (int i = 0; i < 2; ++i) mbar_init(&ctl.acc_full[i], 1), mbar_init(&ctl.acc_empty[i], kEpilogueWarps);
+        for (int i = 0; i < kBS; ++i) mbar_init(&ctl.full[i], 1 + kDequantWarps / 2), mbar_init(&ctl.consumed[i], 2);  // one commit per MMA warp
+        for (int i = 0; i < 2; ++i) mbar_init(&ctl.acc_full[i], 2), mbar_init(&ctl.acc_empty[i], kEpilogueWarps);
         ctl.abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -203,10 +203,12 @@ __global__ void __launch_bounds__(kThreads, 1)
             atomicAdd(&g_prefill_cycles[MODE * 16 + 1], (unsigned long long)waited[0]);
             atomicAdd(&g_prefill_cycles[MODE * 16 + 2], (unsigned long long)waited[1]);
         }
-    } else if (warp == kMmaWarp) {
-        // ---- MMA issuer ----
+    } else if (warp >= kMmaWarp) {
+        // ---- MMA issuers: one warp per accumulator. A tcgen05.mma occupies its issuing thread ~100 cycles whatever N <= 128
+        //      is; two threads issuing into different accumulators run at twice that rate. ----
+        const int acc = warp - kMmaWarp;
         uint32_t kc = 0, it = 0;
-        bool ok = true;
+        bool ok = true, peeked = false;
         long long waited[3] = {0, 0, 0};
         for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x, ++it) {
             const int32_t *t = a.tiles + 1 + 3 * (w / a.RB);
@@ -219,7 +221,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             tc_fence_after();
             for (int kb = 0; kb < nkb && ok; ++kb, ++kc) {
                 const int sa = kc % kAS, sb_ = kc % kBS;
-                if (lane == 0) TIMED_WAIT(1, mbar_wait(&ctl.full[sb_], (kc / kBS) & 1u, abort_flag));
+                if (lane == 0 && !peeked) TIMED_WAIT(1, mbar_wait(&ctl.full[sb_], (kc / kBS) & 1u, abort_flag));
                 ok = __shfl_sync(0xffffffffu, ok, 0);
                 if (!ok) break;
                 tc_fence_after();
@@ -227,18 +229,17 @@ __global__ void __launch_bounds__(kThreads, 1)
                     const uint32_t a0 = tmem + kAColBase + sa * kAStageCols, b0 = smem_u32(b_stages + sb_ * kBTile);
 #pragma unroll
                     for (int k = 0; k < kBK / 16; ++k)  // 16 K elements = 8 packed columns of A, 32 bytes of a B row
-#pragma unroll
-                        for (int acc = 0; acc < 2; ++acc)
-                            umma_f16_ts(tmem + buf * kBufCols + acc * kAccCols, a0 + acc * 32 + k * 8, umma_desc(b0 + k * 32), idesc,
-                                        (kb | k) ? 1u : 0u);
-                    umma_commit(&ctl.consumed[sb_]);  // one commit per K block: it frees this token stage and the A stage
+                        umma_f16_ts(tmem + buf * kBufCols + acc * kAccCols, a0 + acc * 32 + k * 8, umma_desc(b0 + k * 32), idesc, (kb | k) ? 1u : 0u);
+                    // one commit per K block and issuer (together they free the token stage and the A stage), and a first look at
+                    // the next K block's barrier
+                    peeked = umma_commit_and_peek(&ctl.consumed[sb_], &ctl.full[(kc + 1) % kBS], ((kc + 1) / kBS) & 1u);
                 }
                 __syncwarp();
             }
             if (lane == 0 && ok) umma_commit(&ctl.acc_full[buf]);
             __syncwarp();
         }
-        if (lane == 0)
+        if (lane == 0 && acc == 0)
             for (int i = 0; i < 3; ++i) atomicAdd(&g_prefill_cycles[MODE * 16 + 3 + i], (unsigned long long)waited[i]);
         tc_fence_before();
     } else if (warp < kDequantWarps) {
