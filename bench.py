@@ -194,7 +194,7 @@ def build_ring(cfg, rank, device):
                 bias = (np.random.default_rng(seed + 7).standard_normal(cfg["E"]) * cfg["bias"]).astype(np.float32)
             layers.append(synth.make_layer(seed, cfg["d"], cfg["I"], cfg["E"], cfg["k"], act, G=G_EXPERTS, router=cfg["router"], shared=cfg["shared"],
                                            mix=cfg["mix"], bias=bias, max_tokens=cfg["M"], grouped_min_tokens=cfg.get("grouped_min", 6),
-                                           math=cfg.get("math", 0), decode_impl=cfg.get("decode_impl", 0), device=device))
+                                           math=cfg.get("math", 0), decode_impl=cfg.get("decode_impl", 0), tensor_min_tokens=cfg.get("tensor_min_tokens", 0), device=device))
         g.manual_seed(7000 + 100 * rank + r)
         x = torch.randn((cfg["M"], cfg["d"]), generator=g, device=device, dtype=torch.float32)
         x = x if cfg["act"] == "f32" else x.to(torch.bfloat16)
@@ -416,10 +416,15 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--ring", type=int, default=0, help="override the number of independent (weights, tokens) pairs cycled (a small ring keeps a profiler capture small)")
+    ap.add_argument("--tensor-min-tokens", type=int, default=0, help="with --math 2: run forwards of at least this many tokens on the tensor-core path")
+    ap.add_argument("--math", type=int, default=-1, choices=[-1, 0, 1, 2], help="override the workload's MoeMath (0 = FP32 kernels, 1/2 = tensor cores)")
     ap.add_argument("--decode-impl", type=int, default=0, choices=[0, 1], help="forwards of <= 8 tokens: 0 = the fused kernel, 1 = the per-function kernels")
     args = ap.parse_args()
     cfg = dict(WORKLOADS[args.workload])
     cfg["decode_impl"] = args.decode_impl
+    cfg["tensor_min_tokens"] = args.tensor_min_tokens
+    if args.math >= 0:
+        cfg["math"] = args.math
     if args.ring > 0:
         cfg["ring"] = args.ring
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))

@@ -241,6 +241,8 @@ typedef struct strix_moe_layer_desc {
     int64_t max_tokens;
     int64_t grouped_min_tokens; /* the grouped path runs from this many tokens (reference: 6, runtime/qwen4exp.hpp:266) */
     int math;                   /* STRIX_MATH_* of the grouped path */
+    int64_t tensor_min_tokens;  /* math != STRIX_MATH_F32: forwards of at least this many tokens run the tensor-core path
+                                 * (0 = the default, 64); below it the FP32 kernels run */
     int decode_impl;            /* forwards of <= 8 tokens: 0 = the fused single-kernel path where the shapes allow it,
                                  * 1 = the per-function kernels in the reference's sequence */
 } strix_moe_layer_desc;

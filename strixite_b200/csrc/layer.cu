@@ -74,6 +74,7 @@ struct strix_moe_layer {
     sb::DecodeParams plan{};
     // the tensor-core path for many tokens (math != F32, uniform 4-bit stacks)
     sb::PrefillPlan *prefill = nullptr;
+    int64_t tensor_min = 64;
 };
 
 namespace {
@@ -194,7 +195,8 @@ int strix_moe_layer_create(const strix_moe_layer_desc *desc, strix_moe_layer **o
             if (rc == 0 && cudaMemset(L->sync, 0, 512) != cudaSuccess) rc = STRIX_ERR_CUDA;
         }
     }
-    if (rc == 0 && d.math != STRIX_MATH_F32 && sb::prefill_supported(d) && T >= kPrefillMinTokens)
+    L->tensor_min = d.tensor_min_tokens > 0 ? d.tensor_min_tokens : kPrefillMinTokens;
+    if (rc == 0 && d.math != STRIX_MATH_F32 && sb::prefill_supported(d) && T >= L->tensor_min)
         rc = sb::prefill_create(d, L->A, L->Estack, L->router_rows, &L->prefill);
     if (rc == 0 && cudaMemset(L->err, 0, 32) != cudaSuccess) rc = STRIX_ERR_CUDA;
     if (rc == 0 && cudaMallocHost(&L->pin_x, (size_t)(T * d.d * es)) != cudaSuccess) rc = STRIX_ERR_CUDA;
@@ -239,7 +241,7 @@ int strix_moe_layer_forward(strix_moe_layer *L, const void *x, int64_t M, void *
     uint32_t *router_err = L->err, *expert_err = L->err + 3;
     L->last_M = M;
 
-    if (L->fused_ok && M <= 8) {
+    if (L->fused_ok && M <= 8 && !(L->prefill != nullptr && M >= L->tensor_min)) {
         // Decode / verify: the whole sublayer in one persistent kernel.
         sb::DecodeParams p = L->plan;
         p.M = (int)M, p.x = x, p.y = y;
@@ -258,7 +260,7 @@ int strix_moe_layer_forward(strix_moe_layer *L, const void *x, int64_t M, void *
         return 0;
     }
     // 1. Router logits, FP32 [M, R]; row E (when gated) is the shared expert's gate.
-    const bool tensor_path = L->prefill != nullptr && M >= kPrefillMinTokens;
+    const bool tensor_path = L->prefill != nullptr && M >= L->tensor_min;
     const bool dense_router = tensor_path && sb::prefill_has_dense_router(L->prefill);
     if (dense_router) SB_TRY(sb::prefill_router_logits(L->prefill, x, M, L->logits, d.router_bias, E, st));  // bias added in its epilogue
     else if (d.router_kind == STRIX_ROUTER_Q) SB_TRY(linear_any(d.router_bits, x, &d.router_q, L->logits, M, act, STRIX_ACT_F32, stream));
@@ -325,8 +327,7 @@ int strix_moe_layer_forward(strix_moe_layer *L, const void *x, int64_t M, void *
 int strix_moe_layer_experts_partial(strix_moe_layer *L, const void *rows, const int32_t *ids, int64_t n, float *partial, void *stream) {
     const char *fn = "moe_layer_experts_partial";
     SB_CHECK(L != nullptr && rows != nullptr && ids != nullptr && partial != nullptr, fn, ": null pointer");
-    SB_CHECK(L->prefill != nullptr, fn, ": the layer has no tensor-core plan (needs math != F32, uniform 4-bit stacks, d % 256 == 0, I % 128 == 0 and max_tokens >= ",
-             kPrefillMinTokens, ")");
+    SB_CHECK(L->prefill != nullptr, fn, ": the layer has no tensor-core plan (needs math != F32, uniform 4-bit stacks, d % 256 == 0, I % 128 == 0 and max_tokens >= tensor_min_tokens)");
     SB_CHECK(n >= 1 && n <= L->d.max_tokens * L->A, fn, ": ", n, " rows, expected 1..", L->d.max_tokens * L->A);
     auto st = static_cast<cudaStream_t>(stream);
     SB_TRY(strix_moe_group_routes(ids, n, 1, L->Estack, L->group_ws, L->group_ws_bytes, L->err + 3, stream));

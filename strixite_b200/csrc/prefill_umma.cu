@@ -57,35 +57,50 @@ __device__ unsigned long long g_prefill_cycles[32];
 
 constexpr int kBK = 64;                 // K per stage: 64 F16 = one 128-byte swizzle row
 constexpr int kTile = kTileM * kBK * 2;  // 16 KB: 128 rows x 64 F16 (the dense projection's operand tiles)
-constexpr int kTileSlots = 96;          // routed slots per tile = MMA N at most
-constexpr int kBTile = kTileSlots * kBK * 2;  // 12 KB: the token tile of one K block
-constexpr int kBS = 6;                  // token-tile stages
 constexpr int kRS = 6;                  // raw stages: 2 x (128 rows x 64 bytes) = 128 codes of 256 rows
 constexpr int kRawTile = kTileM * 64;
 constexpr int kRawStage = 2 * kRawTile;
-constexpr int kAS = 2;                  // A stages in tensor memory: 2 accumulators x 32 columns (64 F16 per row) each
-// tensor-memory columns: two accumulator buffers of 2 x 96 FP32 columns, then the A stages
-constexpr int kAccCols = kTileSlots, kBufCols = 2 * kAccCols, kAColBase = 2 * kBufCols, kAStageCols = 64;
-static_assert(kAColBase + kAS * kAStageCols <= 512, "tensor memory has 512 columns");
-constexpr int kDequantWarps = 16, kEpilogueWarps = 8;
-constexpr int kProducerWarp = kDequantWarps + kEpilogueWarps, kMmaWarp = kProducerWarp + 1;  // warps kMmaWarp and kMmaWarp + 1 issue MMAs
-constexpr int kThreads = (kMmaWarp + 2) * 32;
+constexpr int kAStageCols = 64;         // an A stage in tensor memory: 2 row halves x 32 columns (64 F16 per row)
+constexpr int kDequantWarps = 16;
+constexpr int64_t kSmallSlots = 1024;    // forwards with at most this many routed slots use the small-tile kernels
 
+// Two shapes of the FFN kernel. WIDE (many tokens): tiles of up to 96 slots, two accumulators (the work item's two row
+// halves), one MMA-issuing warp each. SMALL (a handful of tokens: decode, verify): tiles of up to 32 slots, and each row
+// half's K block split between two accumulators and two issuing warps (an instruction occupies its issuing thread ~100
+// cycles whatever N is, so with N = 16 the issue rate is all that matters; the epilogue adds the two halves in a fixed
+// order), a deeper A ring in the tensor-memory columns the narrow accumulators leave free.
+template <bool SMALL>
+struct FC {
+    static constexpr int TileSlots = SMALL ? 32 : 96;          // routed slots per tile = MMA N at most
+    static constexpr int BTile = TileSlots * kBK * 2;         // the token tile of one K block
+    static constexpr int BS = SMALL ? 8 : 6;                  // token-tile stages (= ready / consumed barriers)
+    static constexpr int KSplit = SMALL ? 2 : 1;              // accumulators (and issuing warps) per row half
+    static constexpr int NAcc = 2 * KSplit;
+    static constexpr int AccCols = TileSlots, BufCols = NAcc * AccCols, AColBase = 2 * BufCols;
+    static constexpr int AS = SMALL ? 4 : 2;                  // A stages in tensor memory
+    static constexpr int EpiWarps = SMALL ? 4 : 8;
+    static constexpr int ProducerWarp = kDequantWarps + EpiWarps, MmaWarp = ProducerWarp + 1;  // NAcc issuing warps from MmaWarp on
+    static constexpr int Threads = (MmaWarp + NAcc) * 32;
+    static_assert(AColBase + AS * kAStageCols <= 512, "tensor memory has 512 columns");
+    static_assert(AS <= BS, "an A stage is freed through the barrier of the K block that used it");
+};
+
+template <bool SMALL>
 struct Ctl {
-    uint64_t raw_full[kRS], raw_empty[kRS], full[kBS], consumed[kBS], acc_full[2], acc_empty[2];
+    uint64_t raw_full[kRS], raw_empty[kRS], full[FC<SMALL>::BS], consumed[FC<SMALL>::BS], acc_full[2], acc_empty[2];
     uint32_t tmem_base;
     int abort_flag;
 };
 
 // ---------------------------------------------------------------------------------------------------------------
 // tiles[0] = number of tiles, then (bucket, first sorted position, slots) per tile; buckets in ascending order.
-__global__ void __launch_bounds__(1024) tiles_kernel(const int32_t *ws, int32_t *tiles) {
+__global__ void __launch_bounds__(1024) tiles_kernel(const int32_t *ws, int32_t *tiles, int tile_slots) {
     __shared__ int32_t scan[1024];
     const int32_t S = ws[1], E = ws[2];
     const RouteTables rt = route_tables(ws, S, E);
     const int e = threadIdx.x;
     const int32_t cnt = e < E ? rt.offsets[e + 1] - rt.offsets[e] : 0;
-    const int32_t nt = (cnt + kTileSlots - 1) / kTileSlots;
+    const int32_t nt = (cnt + tile_slots - 1) / tile_slots;
     scan[e] = nt;
     __syncthreads();
     for (int off = 1; off < 1024; off <<= 1) {
@@ -97,7 +112,7 @@ __global__ void __launch_bounds__(1024) tiles_kernel(const int32_t *ws, int32_t 
     const int32_t first = scan[e] - nt;
     for (int t = 0; t < nt; ++t) {
         int32_t *o = tiles + 1 + 3 * (first + t);
-        o[0] = e, o[1] = rt.offsets[e] + t * kTileSlots, o[2] = min(kTileSlots, cnt - t * kTileSlots);
+        o[0] = e, o[1] = rt.offsets[e] + t * tile_slots, o[2] = min(tile_slots, cnt - t * tile_slots);
     }
     if (e == 1023) tiles[0] = scan[1023];
 }
@@ -137,25 +152,26 @@ __device__ __forceinline__ float swiglu_rounded(float g, float u, bool bf16) {
     return __fdividef(g, 1.0f + __expf(-g)) * u;
 }
 
-template <int MODE, int G>
-__global__ void __launch_bounds__(kThreads, 1)
+template <int MODE, int G, bool SMALL>
+__global__ void __launch_bounds__(FC<SMALL>::Threads, 1)
     ffn_umma_kernel(const __grid_constant__ CUtensorMap raw_map, const __grid_constant__ CUtensorMap b_map, const FfnArgs a) {
+    using C = FC<SMALL>;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t *base = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-    uint8_t *b_stages = base, *raws = b_stages + kBS * kBTile;
-    Ctl &ctl = *reinterpret_cast<Ctl *>(raws + kRS * kRawStage);
+    uint8_t *b_stages = base, *raws = b_stages + C::BS * C::BTile;
+    Ctl<SMALL> &ctl = *reinterpret_cast<Ctl<SMALL> *>(raws + kRS * kRawStage);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const long long t_kernel = clock64();
     if (tid == 0) {
         for (int i = 0; i < kRS; ++i) mbar_init(&ctl.raw_full[i], 1), mbar_init(&ctl.raw_empty[i], kDequantWarps);
-        // full[kc % kBS]: K block kc is ready = its token tile has landed (the producer's arrival + bytes) and the 8 dequantizer
-        // warps of its half have stored the A stage
-        for (int i = 0; i < kBS; ++i) mbar_init(&ctl.full[i], 1 + kDequantWarps / 2), mbar_init(&ctl.consumed[i], 2);  // one commit per MMA warp
-        for (int i = 0; i < 2; ++i) mbar_init(&ctl.acc_full[i], 2), mbar_init(&ctl.acc_empty[i], kEpilogueWarps);
+        // full[kc % BS]: K block kc is ready = its token tile has landed (the producer's arrival + bytes) and the 8 dequantizer
+        // warps of its half have stored the A stage; consumed[kc % BS]: every issuing warp has committed its MMAs of K block kc
+        for (int i = 0; i < C::BS; ++i) mbar_init(&ctl.full[i], 1 + kDequantWarps / 2), mbar_init(&ctl.consumed[i], C::NAcc);
+        for (int i = 0; i < 2; ++i) mbar_init(&ctl.acc_full[i], C::NAcc), mbar_init(&ctl.acc_empty[i], C::EpiWarps);
         ctl.abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == kMmaWarp) {
+    if (warp == C::MmaWarp) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctl.tmem_base)), "r"(512u) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -167,12 +183,12 @@ __global__ void __launch_bounds__(kThreads, 1)
     const int nkb = a.K / kBK;
     volatile int *abort_flag = &ctl.abort_flag;
 
-    // stack row of accumulator `acc`, row 0, of a work item
+    // stack row of row half `acc`, row 0, of a work item
     auto first_row = [&](int bucket, int rb, int acc) {
         return MODE == 0 ? bucket * a.rows_per_expert + acc * a.I + rb * kTileM : bucket * a.rows_per_expert + rb * 2 * kTileM + acc * kTileM;
     };
 
-    if (warp == kProducerWarp) {
+    if (warp == C::ProducerWarp) {
         // ---- TMA producer ----
         if (lane == 0) {
             uint32_t rawc = 0, bc = 0;
@@ -192,21 +208,22 @@ __global__ void __launch_bounds__(kThreads, 1)
                         tma_load_2d(raws + rs * kRawStage + kRawTile, &raw_map, (kb >> 1) * 64, r1, &ctl.raw_full[rs]);
                         ++rawc;
                     }
-                    const int s = bc % kBS;
-                    TIMED_WAIT(1, mbar_wait(&ctl.consumed[s], ((bc / kBS) & 1u) ^ 1u, abort_flag));  // K block bc - kBS is done
+                    const int s = bc % C::BS;
+                    TIMED_WAIT(1, mbar_wait(&ctl.consumed[s], ((bc / C::BS) & 1u) ^ 1u, abort_flag));  // K block bc - BS is done
                     if (!ok) break;
-                    mbar_expect_tx(&ctl.full[s], kBTile);
-                    tma_load_2d(b_stages + s * kBTile, &b_map, kb * kBK, start, &ctl.full[s]);
+                    mbar_expect_tx(&ctl.full[s], C::BTile);
+                    tma_load_2d(b_stages + s * C::BTile, &b_map, kb * kBK, start, &ctl.full[s]);
                     ++bc;
                 }
             }
             atomicAdd(&g_prefill_cycles[MODE * 16 + 1], (unsigned long long)waited[0]);
             atomicAdd(&g_prefill_cycles[MODE * 16 + 2], (unsigned long long)waited[1]);
         }
-    } else if (warp >= kMmaWarp) {
-        // ---- MMA issuers: one warp per accumulator. A tcgen05.mma occupies its issuing thread ~100 cycles whatever N <= 128
-        //      is; two threads issuing into different accumulators run at twice that rate. ----
-        const int acc = warp - kMmaWarp;
+    } else if (warp >= C::MmaWarp) {
+        // ---- MMA issuers: one warp per accumulator = (row half, K part). A tcgen05.mma occupies its issuing thread ~100 cycles
+        //      whatever N <= 128 is; threads issuing into different accumulators run in parallel. ----
+        const int ai = warp - C::MmaWarp, acc = ai / C::KSplit, kpart = ai % C::KSplit;
+        constexpr int KSteps = (kBK / 16) / C::KSplit;  // 16-element K steps of a K block per issuer
         uint32_t kc = 0, it = 0;
         bool ok = true, peeked = false;
         long long waited[3] = {0, 0, 0};
@@ -220,30 +237,33 @@ __global__ void __launch_bounds__(kThreads, 1)
             if (!ok) break;
             tc_fence_after();
             for (int kb = 0; kb < nkb && ok; ++kb, ++kc) {
-                const int sa = kc % kAS, sb_ = kc % kBS;
-                if (lane == 0 && !peeked) TIMED_WAIT(1, mbar_wait(&ctl.full[sb_], (kc / kBS) & 1u, abort_flag));
+                const int sa = kc % C::AS, sb_ = kc % C::BS;
+                if (lane == 0 && !peeked) TIMED_WAIT(1, mbar_wait(&ctl.full[sb_], (kc / C::BS) & 1u, abort_flag));
                 ok = __shfl_sync(0xffffffffu, ok, 0);
                 if (!ok) break;
                 tc_fence_after();
                 if (lane == 0) {
-                    const uint32_t a0 = tmem + kAColBase + sa * kAStageCols, b0 = smem_u32(b_stages + sb_ * kBTile);
+                    const uint32_t a0 = tmem + C::AColBase + sa * kAStageCols + acc * 32, b0 = smem_u32(b_stages + sb_ * C::BTile);
+                    const uint32_t d0 = tmem + buf * C::BufCols + ai * C::AccCols;
 #pragma unroll
-                    for (int k = 0; k < kBK / 16; ++k)  // 16 K elements = 8 packed columns of A, 32 bytes of a B row
-                        umma_f16_ts(tmem + buf * kBufCols + acc * kAccCols, a0 + acc * 32 + k * 8, umma_desc(b0 + k * 32), idesc, (kb | k) ? 1u : 0u);
+                    for (int j = 0; j < KSteps; ++j) {  // 16 K elements = 8 packed columns of A, 32 bytes of a B row
+                        const int k = kpart * KSteps + j;
+                        umma_f16_ts(d0, a0 + k * 8, umma_desc(b0 + k * 32), idesc, (kb | j) ? 1u : 0u);
+                    }
                     // one commit per K block and issuer (together they free the token stage and the A stage), and a first look at
                     // the next K block's barrier
-                    peeked = umma_commit_and_peek(&ctl.consumed[sb_], &ctl.full[(kc + 1) % kBS], ((kc + 1) / kBS) & 1u);
+                    peeked = umma_commit_and_peek(&ctl.consumed[sb_], &ctl.full[(kc + 1) % C::BS], ((kc + 1) / C::BS) & 1u);
                 }
                 __syncwarp();
             }
             if (lane == 0 && ok) umma_commit(&ctl.acc_full[buf]);
             __syncwarp();
         }
-        if (lane == 0 && acc == 0)
+        if (lane == 0 && ai == 0)
             for (int i = 0; i < 3; ++i) atomicAdd(&g_prefill_cycles[MODE * 16 + 3 + i], (unsigned long long)waited[i]);
         tc_fence_before();
     } else if (warp < kDequantWarps) {
-        // ---- dequantizers: thread = (K block half kbl, accumulator acc, row r): 64 codes of one row per raw stage ----
+        // ---- dequantizers: thread = (K block half kbl, row half acc, row r): 64 codes of one row per raw stage ----
         const int r = tid & 127, acc = (tid >> 7) & 1, kbl = tid >> 8;
         const int gpr = a.K / G;
         constexpr int NG = G >= 64 ? 1 : 64 / G;  // groups in a thread's 64 codes
@@ -269,7 +289,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                 for (int j = 0; j < 2; ++j) c[j] = *reinterpret_cast<const uint4 *>(rt + (((kbl * 2 + j) ^ ((r >> 1) & 3)) << 4));
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&ctl.raw_empty[rs]);  // the codes are in registers
-                uint32_t av[32];  // 64 F16 of this row: tensor-memory columns 0..31 of the stage's accumulator half
+                uint32_t av[32];  // 64 F16 of this row: tensor-memory columns 0..31 of the stage's row half
 #pragma unroll
                 for (int u = 0; u < 8; ++u) {
                     const uint4 q = c[u >> 2];
@@ -280,17 +300,17 @@ __global__ void __launch_bounds__(kThreads, 1)
                 }
                 // converted first: only the store into tensor memory waits for the stage
                 const uint32_t kc = rawc * 2 + kbl;  // the K block this thread feeds
-                const int s = kc % kAS;
-                if (kc >= kAS) {  // the stage is free once K block kc - kAS has been consumed
-                    const uint32_t pc = kc - kAS;
-                    TIMED_WAIT(1, mbar_wait(&ctl.consumed[pc % kBS], (pc / kBS) & 1u, abort_flag));
+                const int s = kc % C::AS;
+                if (kc >= (uint32_t)C::AS) {  // the stage is free once K block kc - AS has been consumed
+                    const uint32_t pc = kc - C::AS;
+                    TIMED_WAIT(1, mbar_wait(&ctl.consumed[pc % C::BS], (pc / C::BS) & 1u, abort_flag));
                     if (!ok) break;
                 }
-                tmem_st32(tmem + ((uint32_t)(r & ~31) << 16) + kAColBase + s * kAStageCols + acc * 32, av);
+                tmem_st32(tmem + ((uint32_t)(r & ~31) << 16) + C::AColBase + s * kAStageCols + acc * 32, av);
                 tmem_st_wait();
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&ctl.full[kc % kBS]);
+                if (lane == 0) mbar_arrive(&ctl.full[kc % C::BS]);
             }
         }
         if (tid == 0) {
@@ -299,8 +319,9 @@ __global__ void __launch_bounds__(kThreads, 1)
             atomicAdd(&g_prefill_cycles[MODE * 16 + 8], (unsigned long long)(clock64() - t_start));
         }
     } else {
-        // ---- epilogue: 8 warps; lane quadrant q = warp % 4, the two warps of a quadrant take alternate 16-column chunks ----
+        // ---- epilogue: lane quadrant q = warp % 4; with 8 warps the two of a quadrant take alternate 16-column chunks ----
         const int ew = warp - kDequantWarps, q = ew & 3, half = ew >> 2, r = q * 32 + lane;
+        constexpr int ChunkStride = 16 * (C::EpiWarps / 4);
         const RouteTables rtab = route_tables(a.ws, a.ws[1], a.ws[2]);
         uint32_t it = 0;
         bool ok = true;
@@ -313,12 +334,23 @@ __global__ void __launch_bounds__(kThreads, 1)
             TIMED_WAIT(0, mbar_wait(&ctl.acc_full[buf], (it >> 1) & 1u, abort_flag));
             if (!ok) break;
             tc_fence_after();
-            const uint32_t tbase = tmem + ((uint32_t)(q * 32) << 16) + buf * kBufCols;
-            for (int c0 = half * 16; c0 < n_valid; c0 += 32) {
+            const uint32_t tbase = tmem + ((uint32_t)(q * 32) << 16) + buf * C::BufCols;
+            for (int c0 = half * 16; c0 < n_valid; c0 += ChunkStride) {
                 uint32_t v0[16], v1[16];
                 tmem_ld16(tbase + c0, v0);
-                tmem_ld16(tbase + kAccCols + c0, v1);
+                tmem_ld16(tbase + C::KSplit * C::AccCols + c0, v1);
                 tmem_ld_wait();
+                if constexpr (C::KSplit == 2) {  // the second K part of each row half, added in a fixed order
+                    uint32_t w0[16], w1[16];
+                    tmem_ld16(tbase + C::AccCols + c0, w0);
+                    tmem_ld16(tbase + 3 * C::AccCols + c0, w1);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        v0[j] = __float_as_uint(__uint_as_float(v0[j]) + __uint_as_float(w0[j]));
+                        v1[j] = __float_as_uint(__uint_as_float(v1[j]) + __uint_as_float(w1[j]));
+                    }
+                }
                 if (MODE == 0) {
                     const int i = rb * kTileM + r;  // intermediate column
                     const int pos = (i & ~7) + ((i & 3) << 1) + ((i >> 2) & 1);
@@ -354,7 +386,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     __syncthreads();
     if (tid == 0) atomicAdd(&g_prefill_cycles[MODE * 16], (unsigned long long)(clock64() - t_kernel));
     if (tid == 0 && ctl.abort_flag) atomicAdd(&g_prefill_aborts, 1u);
-    if (warp == kMmaWarp) {
+    if (warp == C::MmaWarp) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
     }
@@ -480,24 +512,29 @@ int make_map(const char *fn, CUtensorMap *m, CUtensorMapDataType dt, int es, con
     return 0;
 }
 
-constexpr size_t kFfnSmem = (size_t)kBS * kBTile + (size_t)kRS * kRawStage + sizeof(Ctl) + 1024;
+template <bool SMALL>
+constexpr size_t ffn_smem() {
+    return (size_t)FC<SMALL>::BS * FC<SMALL>::BTile + (size_t)kRS * kRawStage + sizeof(Ctl<SMALL>) + 1024;
+}
 constexpr size_t kDenseSmem = (size_t)kDS * 2 * kTile + sizeof(DenseCtl) + 1024;
 
-template <int MODE>
+template <int MODE, bool SMALL>
 int launch_ffn(const char *fn, int G, const CUtensorMap &raw, const CUtensorMap &b, const FfnArgs &a, int ctas, cudaStream_t st) {
-    static thread_local int prepared = -1;  // one per MODE and host thread
+    static thread_local int prepared = -1;  // one per (MODE, SMALL) and host thread
+    constexpr size_t smem = ffn_smem<SMALL>();
+    constexpr int threads = FC<SMALL>::Threads;
     int dev = 0;
     SB_CUDA(cudaGetDevice(&dev), fn);
     if (prepared != dev) {
-        SB_CUDA(cudaFuncSetAttribute(ffn_umma_kernel<MODE, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kFfnSmem), fn);
-        SB_CUDA(cudaFuncSetAttribute(ffn_umma_kernel<MODE, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kFfnSmem), fn);
-        SB_CUDA(cudaFuncSetAttribute(ffn_umma_kernel<MODE, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kFfnSmem), fn);
+        SB_CUDA(cudaFuncSetAttribute(ffn_umma_kernel<MODE, 32, SMALL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), fn);
+        SB_CUDA(cudaFuncSetAttribute(ffn_umma_kernel<MODE, 64, SMALL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), fn);
+        SB_CUDA(cudaFuncSetAttribute(ffn_umma_kernel<MODE, 128, SMALL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), fn);
         prepared = dev;
     }
-    if (G == 32) ffn_umma_kernel<MODE, 32><<<ctas, kThreads, kFfnSmem, st>>>(raw, b, a);
-    else if (G == 64) ffn_umma_kernel<MODE, 64><<<ctas, kThreads, kFfnSmem, st>>>(raw, b, a);
-    else ffn_umma_kernel<MODE, 128><<<ctas, kThreads, kFfnSmem, st>>>(raw, b, a);
-    SB_LAUNCH_OK(fn, " (tcgen05 FFN stage ", MODE, ") K=", a.K, " G=", G);
+    if (G == 32) ffn_umma_kernel<MODE, 32, SMALL><<<ctas, threads, smem, st>>>(raw, b, a);
+    else if (G == 64) ffn_umma_kernel<MODE, 64, SMALL><<<ctas, threads, smem, st>>>(raw, b, a);
+    else ffn_umma_kernel<MODE, 128, SMALL><<<ctas, threads, smem, st>>>(raw, b, a);
+    SB_LAUNCH_OK(fn, " (tcgen05 FFN stage ", MODE, SMALL ? ", small tiles" : "", ") K=", a.K, " G=", G);
     return 0;
 }
 
@@ -506,7 +543,7 @@ int launch_ffn(const char *fn, int G, const CUtensorMap &raw, const CUtensorMap 
 namespace sb {
 
 struct PrefillPlan {
-    CUtensorMap gu_raw, dn_raw, xg_map, hs_map, rw_map;
+    CUtensorMap gu_raw, dn_raw, xg_map, hs_map, xg_map_s, hs_map_s, rw_map;  // _s: boxes of 32 rows for the small-tile kernels
     bool dense_router = false;
     int64_t d, I, Estack, max_tokens, A, router_rows;
     int G_gu, G_dn;
@@ -537,11 +574,13 @@ int prefill_create(const strix_moe_layer_desc &d, int64_t A, int64_t Estack, int
     };
     alloc(reinterpret_cast<void **>(&p->xg), (size_t)S * d.d * 2);
     alloc(reinterpret_cast<void **>(&p->hs), (size_t)S * d.I * 2);
-    alloc(reinterpret_cast<void **>(&p->tiles), (size_t)(1 + 3 * (S / kTileSlots + Estack + 2)) * 4);
+    alloc(reinterpret_cast<void **>(&p->tiles), (size_t)(1 + 3 * (S / FC<true>::TileSlots + Estack + 2)) * 4);
     if (rc == 0) rc = make_map(fn, &p->gu_raw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, d.gate_up.q, Estack * 2 * d.I, d.d / 2, 64, CU_TENSOR_MAP_SWIZZLE_64B);
     if (rc == 0) rc = make_map(fn, &p->dn_raw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, d.down.q, Estack * d.d, d.I / 2, 64, CU_TENSOR_MAP_SWIZZLE_64B);
-    if (rc == 0) rc = make_map(fn, &p->xg_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, p->xg, S, d.d, kBK, CU_TENSOR_MAP_SWIZZLE_128B, kTileSlots);
-    if (rc == 0) rc = make_map(fn, &p->hs_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, p->hs, S, d.I, kBK, CU_TENSOR_MAP_SWIZZLE_128B, kTileSlots);
+    if (rc == 0) rc = make_map(fn, &p->xg_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, p->xg, S, d.d, kBK, CU_TENSOR_MAP_SWIZZLE_128B, FC<false>::TileSlots);
+    if (rc == 0) rc = make_map(fn, &p->hs_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, p->hs, S, d.I, kBK, CU_TENSOR_MAP_SWIZZLE_128B, FC<false>::TileSlots);
+    if (rc == 0) rc = make_map(fn, &p->xg_map_s, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, p->xg, S, d.d, kBK, CU_TENSOR_MAP_SWIZZLE_128B, FC<true>::TileSlots);
+    if (rc == 0) rc = make_map(fn, &p->hs_map_s, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, p->hs, S, d.I, kBK, CU_TENSOR_MAP_SWIZZLE_128B, FC<true>::TileSlots);
     p->dense_router = d.act == kBF16 && d.router_kind == STRIX_ROUTER_BF16 && d.d % kBK == 0;
     if (rc == 0 && p->dense_router)
         rc = make_map(fn, &p->rw_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, d.router_w, router_rows, d.d, kBK, CU_TENSOR_MAP_SWIZZLE_128B);
@@ -605,7 +644,9 @@ bool dense_bf16_ok(const void *x, const void *w, int64_t M, int64_t N, int64_t K
 
 int prefill_experts(PrefillPlan *p, const void *x, int act, const int32_t *ws, int64_t M, int64_t A, float *partial, cudaStream_t st) {
     const char *fn = "moe_layer_forward (tensor-core experts)";
-    tiles_kernel<<<1, 1024, 0, st>>>(ws, p->tiles);
+    // a handful of tokens (decode, verify): tiles of 32 slots and four issuing warps; many tokens: tiles of 96 slots
+    const bool small = M * A <= kSmallSlots;
+    tiles_kernel<<<1, 1024, 0, st>>>(ws, p->tiles, small ? FC<true>::TileSlots : FC<false>::TileSlots);
     SB_LAUNCH_OK(fn, ": tiles");
     SB_CHECK(M * A <= p->max_tokens * p->A, fn, ": ", M * A, " slots exceed the layer's ", p->max_tokens * p->A);
     const unsigned gblocks = (unsigned)std::min<int64_t>((M * A + 7) / 8, 148 * 16);
@@ -616,10 +657,12 @@ int prefill_experts(PrefillPlan *p, const void *x, int act, const int32_t *ws, i
     a.ws = ws, a.tiles = p->tiles;
     a.scale = p->gu_scale, a.minv = p->gu_min, a.K = (int)p->d, a.rows_per_expert = (int)(2 * p->I), a.I = (int)p->I, a.RB = (int)(p->I / kTileM);
     a.hs = p->hs, a.partial = nullptr, a.N = 0, a.bf16_act = act == kBF16;
-    SB_TRY(launch_ffn<0>(fn, p->G_gu, p->gu_raw, p->xg_map, a, p->sms, st));
+    if (small) SB_TRY((launch_ffn<0, true>(fn, p->G_gu, p->gu_raw, p->xg_map_s, a, p->sms, st)));
+    else SB_TRY((launch_ffn<0, false>(fn, p->G_gu, p->gu_raw, p->xg_map, a, p->sms, st)));
     a.scale = p->dn_scale, a.minv = p->dn_min, a.K = (int)p->I, a.rows_per_expert = (int)p->d, a.RB = (int)(p->d / (2 * kTileM));
     a.hs = nullptr, a.partial = partial, a.N = (int)p->d;
-    SB_TRY(launch_ffn<1>(fn, p->G_dn, p->dn_raw, p->hs_map, a, p->sms, st));
+    if (small) SB_TRY((launch_ffn<1, true>(fn, p->G_dn, p->dn_raw, p->hs_map_s, a, p->sms, st)));
+    else SB_TRY((launch_ffn<1, false>(fn, p->G_dn, p->dn_raw, p->hs_map, a, p->sms, st)));
     return 0;
 }
 

@@ -23,7 +23,7 @@ class _Desc(C.Structure):
         ("experts_mixed", C.c_int), ("gate_up_bits", C.c_int), ("down_bits", C.c_int),
         ("gate_up", QView), ("down", QView), ("gate_up_mix", QMixView), ("down_mix", QMixView),
         ("sh_gate_up_bits", C.c_int), ("sh_down_bits", C.c_int), ("sh_gate_up", QView), ("sh_down", QView),
-        ("max_tokens", C.c_int64), ("grouped_min_tokens", C.c_int64), ("math", C.c_int), ("decode_impl", C.c_int),
+        ("max_tokens", C.c_int64), ("grouped_min_tokens", C.c_int64), ("math", C.c_int), ("tensor_min_tokens", C.c_int64), ("decode_impl", C.c_int),
     ]
 
 
@@ -55,7 +55,7 @@ class MoeLayer:
     """
 
     def __init__(self, d, I, E, k, act, router, gate_up, down, shared=None, shared_coef="sigmoid", sh_gate_up=None, sh_down=None,
-                 router_bias=None, max_tokens=8, grouped_min_tokens=kGroupedMinTokens, math=K.MoeMath.F32, decode_impl=0):
+                 router_bias=None, max_tokens=8, grouped_min_tokens=kGroupedMinTokens, math=K.MoeMath.F32, decode_impl=0, tensor_min_tokens=0):
         self._keep = [router, gate_up, down, sh_gate_up, sh_down, router_bias]  # the views must outlive the layer
         self.d, self.I, self.E, self.k, self.act, self.max_tokens = d, I, E, k, K.Act(act), max_tokens
         self.A = k + (1 if shared == "stacked" else 0)
@@ -81,6 +81,7 @@ class MoeLayer:
         if shared == "separate":
             ds.sh_gate_up_bits, ds.sh_down_bits, ds.sh_gate_up, ds.sh_down = sh_gate_up.bits, sh_down.bits, sh_gate_up.view(), sh_down.view()
         ds.max_tokens, ds.grouped_min_tokens, ds.math, ds.decode_impl = max_tokens, grouped_min_tokens, int(math), int(decode_impl)
+        ds.tensor_min_tokens = int(tensor_min_tokens)
         self._desc = ds
         h = C.c_void_p()
         call("strix_moe_layer_create", C.byref(ds), C.byref(h))

@@ -56,7 +56,7 @@ def zipf_bias(seed, E, s=1.1):
 
 def make_layer(seed, d, I, E, k, act, G=128, router="f32", shared="stacked", shared_coef="sigmoid", expert_bits=4, mix=None,
                bias=None, shared_bits=8, shared_G=64, max_tokens=8, grouped_min_tokens=6, math=K.MoeMath.F32, device="cuda",
-               decode_impl=0):
+               decode_impl=0, tensor_min_tokens=0):
     """A seeded layer on the device. router: 'f32' | 'bf16' | 'q8'. mix: probabilities for per-expert (4, 5, 6, 8)-bit
     formats, or None for a uniform `expert_bits` stack. bias: None or a float32 numpy [E]. decode_impl: 0 = the fused
     single-kernel path for up to 8 tokens, 1 = the per-function kernels."""
@@ -83,7 +83,7 @@ def make_layer(seed, d, I, E, k, act, G=128, router="f32", shared="stacked", sha
     if bias is not None:
         kw["router_bias"] = torch.from_numpy(np.ascontiguousarray(bias, np.float32)).to(device)
     layer = MoeLayer(d, I, E, k, act, rw, gate_up, down, shared=shared, shared_coef=shared_coef, max_tokens=max_tokens,
-                     grouped_min_tokens=grouped_min_tokens, math=math, decode_impl=decode_impl, **kw)
+                     grouped_min_tokens=grouped_min_tokens, math=math, decode_impl=decode_impl, tensor_min_tokens=tensor_min_tokens, **kw)
     layer.weights = dict(router=rw, gate_up=gate_up, down=down, **kw)
     layer.info = info
     return layer
