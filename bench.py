@@ -190,7 +190,9 @@ def build_ring(cfg, rank, device):
         for l in range(cfg["layers"]):
             seed = 1000 * (rank + 1) + 100 * r + 10 * l
             bias = None
-            if cfg["bias"] is not None:
+            if cfg["bias"] == "zipf":
+                bias = synth.zipf_bias(seed + 7, cfg["E"])
+            elif cfg["bias"] is not None:
                 bias = (np.random.default_rng(seed + 7).standard_normal(cfg["E"]) * cfg["bias"]).astype(np.float32)
             layers.append(synth.make_layer(seed, cfg["d"], cfg["I"], cfg["E"], cfg["k"], act, G=G_EXPERTS, router=cfg["router"], shared=cfg["shared"],
                                            mix=cfg["mix"], bias=bias, max_tokens=cfg["M"], grouped_min_tokens=cfg.get("grouped_min", 6),
@@ -459,8 +461,11 @@ def main():
     if args.impl == "reference":
         # The reference arm: the CPU path on the host cores, a bounded sample per step.
         cfg["ring"] = 1
-        ring = build_ring(cfg, 0, device)
-        base, one = cpu_baseline(ring, cfg, budget_s=3.0)
+        cfg.pop("ep", None)  # the CPU path has no ranks: the whole layer on the host cores
+        sample = min(cfg["M"], 256)  # a bounded sample of the batch per pass
+        cfg_small = dict(cfg, M=sample, math=0)
+        ring = build_ring(cfg_small, 0, device)
+        base, one = cpu_baseline(ring, cfg_small, budget_s=3.0)
         for _ in range(max(0, min(args.warmup, 3) - 1)):
             one()
         k = max(1, min(args.steps, 20))
@@ -468,9 +473,10 @@ def main():
         for _ in range(k):
             one()
         dt = time.perf_counter() - t0
-        v = cfg["M"] * k / dt
+        v = sample * k / dt
         line.update(impl="reference", value=v, steps=k, ms_per_step=1e3 * dt / k, n_gpus=args.gpus, gpu_launches=0,
-                    cpu_baseline=dict(value=v, unit="tokens/s", cores=base["cores"], kind="port", sample="%d timed passes of %d token(s), one layer set" % (k, cfg["M"])),
+                    cpu_baseline=dict(value=v, unit="tokens/s", cores=base["cores"], kind="port",
+                                      sample="%d timed passes of %d token(s) of the batch, one layer set" % (k, sample)),
                     e2e=dict(value=v, unit="tokens/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0))
         print(json.dumps(line))
         return

@@ -42,6 +42,8 @@ constexpr int kThreads = 32 * CW;
 constexpr int kMaxTok = 8;
 constexpr int kMaxGroups = 96;
 constexpr int kMaxSlots = kMaxGroups - 1;
+constexpr int kDnCols = 2;                               // tokens per down-projection stage at most
+constexpr int kMaxDnItems = kMaxGroups + kMaxSlots / 2;  // sum over groups of ceil(tokens / kDnCols)
 constexpr int kMaxDepth = 4;               // stages per warp
 constexpr uint32_t kSpinLimit = 1u << 22;  // polls before a wait gives up (each poll is tens of ns)
 
@@ -112,6 +114,10 @@ struct Smem {
     float rpart[CW][kMaxTok];  // phase 1: half-row partial logits
     int leaders_before[CW + 2];
     int n_groups, col_max, abort_flag;
+    // phase 3 work list: a group's tokens in runs of at most kDnCols, so that a stage holds few h records and every warp
+    // gets a stage (a wide group's weights are fetched once per run)
+    uint8_t dn_group[kMaxDnItems], dn_mask[kMaxDnItems];
+    int n_dn;
     uint32_t failed_mask;        // tokens the router failed (non-finite logits): NaN rows
 };
 
@@ -494,7 +500,34 @@ __device__ void build_groups(const DecodeParams &p, Smem &sm, int tid) {
             const int c = __popc(sm.groups[gi].mask);
             cm = c > cm ? c : cm;
         }
-        sm.col_max = cm;
+        sm.col_max = cm < kDnCols ? cm : kDnCols;
+    }
+    // phase 3 work list, in group order: thread gi owns group gi's runs; positions by a scan over the first 96 threads
+    {
+        static_assert(kMaxGroups <= 96, "the run scan covers three warps");
+        const uint32_t mk0 = tid < sm.n_groups ? sm.groups[tid].mask : 0u;
+        const int runs = (__popc(mk0) + kDnCols - 1) / kDnCols;
+        int incl = runs;
+        if (tid < 96) {
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int v = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += v;
+            }
+            if (lane == 31) sm.leaders_before[warp] = incl;
+        }
+        __syncthreads();
+        if (tid < 96) {
+            int first = incl - runs;
+            for (int w = 0; w < warp; ++w) first += sm.leaders_before[w];
+            uint32_t mk = mk0;
+            for (int n = first; mk; ++n) {
+                uint32_t sub = 0;
+                for (int c = 0; c < kDnCols && mk; ++c) sub |= mk & (0u - mk), mk &= mk - 1;
+                sm.dn_group[n] = (uint8_t)tid, sm.dn_mask[n] = (uint8_t)sub;
+            }
+            if (tid == 95) sm.n_dn = first + runs;
+        }
     }
     __syncthreads();
 }
@@ -533,8 +566,8 @@ __device__ __forceinline__ void gu_issue(const DecodeParams &p, const Group &grp
 
 // The copies of one down stage: 16 consecutive output rows of the group's expert, their scale / min runs, and the h records
 // of the tokens routed to it (ascending token order).
-__device__ __forceinline__ void dn_issue(const DecodeParams &p, const Group &grp, int nb, uint8_t *st, int rs, int sc_off, int sc_bytes,
-                                         int col_off, int lane) {
+__device__ __forceinline__ void dn_issue(const DecodeParams &p, const Group &grp, uint32_t tokens, int nb, uint8_t *st, int rs, int sc_off,
+                                         int sc_bytes, int col_off, int lane) {
     const int I = p.I, M = p.M, A = p.A;
     const int bits = grp.bits[1], gpr = I / grp.G[1];
     const int rb = (int)row_bytes(bits, I), ppr = rb / 16;
@@ -550,7 +583,7 @@ __device__ __forceinline__ void dn_issue(const DecodeParams &p, const Group &grp
     }
     const int cp_n = p.hrec_bytes / 16;
     int ci = 0;
-    for (uint32_t mk = grp.mask; mk; mk &= mk - 1, ++ci) {
+    for (uint32_t mk = tokens; mk; mk &= mk - 1, ++ci) {
         const int m = __ffs(mk) - 1;
         const int slot_i = grp.expert == -2 ? M * A + m : m * A + grp.slot_a[m];
         const uint8_t *src = p.hrec + (int64_t)slot_i * p.hrec_bytes;
@@ -873,7 +906,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_fused_kernel(const __grid_
 
     {
         // ---- phase 3: down projection + combine. The x planes are dead: stages take the whole dynamic area. ----
-        const int NG = sm.n_groups;
+        const int NG = sm.n_dn;  // work items: (group, run of its tokens)
         uint8_t *st3 = xp;
         const int avail3 = p.smem_bytes - (int)(xp - smem_raw);
         const int rs = p.dn_row_stride, sc_off = 16 * rs, sc_bytes = p.dn_scale_bytes;
@@ -893,6 +926,8 @@ __global__ void __launch_bounds__(kThreads, 1) decode_fused_kernel(const __grid_
         int nb_local = 0;
         if ((int)blockIdx.x < n_blocks) nb_local = (n_blocks - 1 - (int)blockIdx.x) / (int)gridDim.x + 1;
         const int part_off = planes * I * 2;  // the partial sums inside an h record
+        for (int i = tid; i < 2 * 32 * 8; i += kThreads) (&sm.red_sh[0][0][0])[i] = 0.f;  // the shared expert's tile is summed by atomic adds
+        __syncthreads();
         {
             const int cw = warp, g = lane >> 2, c = lane & 3;
             uint8_t *my_stages = st3 + (size_t)cw * D * stage_bytes;
@@ -902,8 +937,9 @@ __global__ void __launch_bounds__(kThreads, 1) decode_fused_kernel(const __grid_
                 const int it = cw + n * ACT;
                 if (it < n_total) {
                     const int nbi = it / NG;
-                    dn_issue(p, sm.groups[it - nbi * NG], (int)blockIdx.x + nbi * (int)gridDim.x, my_stages + (size_t)(n % D) * stage_bytes, rs, sc_off,
-                             sc_bytes, col_off, lane);
+                    const int ii = it - nbi * NG;
+                    dn_issue(p, sm.groups[sm.dn_group[ii]], sm.dn_mask[ii], (int)blockIdx.x + nbi * (int)gridDim.x,
+                             my_stages + (size_t)(n % D) * stage_bytes, rs, sc_off, sc_bytes, col_off, lane);
                 }
                 cp_async_commit();
             };
@@ -911,18 +947,20 @@ __global__ void __launch_bounds__(kThreads, 1) decode_fused_kernel(const __grid_
             int n = 0;
             for (int nbi = 0; nbi < nb_local; ++nbi) {
                 const int nb = (int)blockIdx.x + nbi * (int)gridDim.x;
-                float tot[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}}, tot_sh[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+                float tot[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
                 for (int it = cw + n * ACT; cw < ACT && it < (nbi + 1) * NG; it += ACT, ++n) {
                     cp_async_wait(D - 1);
                     __syncwarp();
                     const int slot = n % D;
-                    const Group &grp = sm.groups[it - nbi * NG];
+                    const Group &grp = sm.groups[sm.dn_group[it - nbi * NG]];
+                    const uint32_t gmask = sm.dn_mask[it - nbi * NG];  // the tokens of this stage
                     const int G = grp.G[1], gpr = I / G;
                     const uint8_t *st = my_stages + (size_t)slot * stage_bytes;
                     const uint8_t *rowA = st + g * rs, *rowB = st + (g + 8) * rs;
                     const uint16_t *sc = reinterpret_cast<const uint16_t *>(st + sc_off), *mn = reinterpret_cast<const uint16_t *>(st + sc_off + sc_bytes);
-                    const int np = (!ONEPASS && planes == 2 && (grp.mask >> 4)) ? 2 : 1;
+                    const int np = (!ONEPASS && planes == 2 && (gmask >> 4)) ? 2 : 1;
                     const bool is_sh = grp.expert == -2;
+                    float sh_stage[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
                     const uint8_t *xb[2] = {nullptr, nullptr};
                     const float *hp[2][2] = {{nullptr, nullptr}, {nullptr, nullptr}};
                     float cf[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
@@ -930,13 +968,13 @@ __global__ void __launch_bounds__(kThreads, 1) decode_fused_kernel(const __grid_
                     for (int ps = 0; ps < 2; ++ps) {
                         int tk, pl;
                         column_of<planes>(g, ps, tk, pl);
-                        if (ps < np && tk < M && (grp.mask >> tk & 1u))
-                            xb[ps] = st + col_off + __popc(grp.mask & ((1u << tk) - 1u)) * p.hrec_bytes + pl * I * 2;
+                        if (ps < np && tk < M && (gmask >> tk & 1u))
+                            xb[ps] = st + col_off + __popc(gmask & ((1u << tk) - 1u)) * p.hrec_bytes + pl * I * 2;
 #pragma unroll
                         for (int e = 0; e < 2; ++e) {
                             column_of<planes>(2 * c + e, ps, tk, pl);
-                            if (ps < np && tk < M && (grp.mask >> tk & 1u)) {
-                                hp[ps][e] = reinterpret_cast<const float *>(st + col_off + __popc(grp.mask & ((1u << tk) - 1u)) * p.hrec_bytes + part_off) + pl * (I / 8);
+                            if (ps < np && tk < M && (gmask >> tk & 1u)) {
+                                hp[ps][e] = reinterpret_cast<const float *>(st + col_off + __popc(gmask & ((1u << tk) - 1u)) * p.hrec_bytes + part_off) + pl * (I / 8);
                                 cf[ps][e] = is_sh ? 1.f : sm.coef[tk * A + grp.slot_a[tk]];  // the shared expert's gate comes after its own rounding
                             }
                         }
@@ -981,7 +1019,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_fused_kernel(const __grid_
 #pragma unroll
                             for (int ps = 0; ps < 2; ++ps) {
                                 if (is_sh) {
-                                    tot_sh[ps][0] += v[ps][0], tot_sh[ps][1] += v[ps][1], tot_sh[ps][2] += v[ps][2], tot_sh[ps][3] += v[ps][3];
+                                    sh_stage[ps][0] += v[ps][0], sh_stage[ps][1] += v[ps][1], sh_stage[ps][2] += v[ps][2], sh_stage[ps][3] += v[ps][3];
                                 } else {
                                     tot[ps][0] = fmaf(cf[ps][0], v[ps][0], tot[ps][0]), tot[ps][1] = fmaf(cf[ps][1], v[ps][1], tot[ps][1]);
                                     tot[ps][2] = fmaf(cf[ps][0], v[ps][2], tot[ps][2]), tot[ps][3] = fmaf(cf[ps][1], v[ps][3], tot[ps][3]);
@@ -992,9 +1030,11 @@ __global__ void __launch_bounds__(kThreads, 1) decode_fused_kernel(const __grid_
                     __syncwarp();
                     issue(n + D);
                     if (is_sh) {
-                        float4 *dst = reinterpret_cast<float4 *>(&sm.red_sh[nbi & 1][lane][0]);
-                        dst[0] = make_float4(tot_sh[0][0], tot_sh[0][1], tot_sh[0][2], tot_sh[0][3]);
-                        dst[1] = make_float4(tot_sh[1][0], tot_sh[1][1], tot_sh[1][2], tot_sh[1][3]);
+                        // the shared expert's runs cover disjoint tokens = disjoint accumulator columns: every word of the tile gets
+                        // one non-zero addend (the others add 0), so the sum does not depend on the order of the adds
+                        float *dst = &sm.red_sh[nbi & 1][lane][0];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) atomicAdd(dst + i, sh_stage[0][i]), atomicAdd(dst + 4 + i, sh_stage[1][i]);
                     }
                 }
                 const int par = nbi & 1;
@@ -1020,7 +1060,8 @@ __global__ void __launch_bounds__(kThreads, 1) decode_fused_kernel(const __grid_
                         T *y = static_cast<T *>(p.y);
                         if (p.shared_mode == STRIX_SHARED_SEPARATE) {  // y = stored(routed) + gate * stored(shared), as moe_shared_add
                             float sv = sm.red_sh[par][ln][rg];
-                            if (planes == 2) sv += sm.red_sh[par][ln + 2][rg];
+                            sm.red_sh[par][ln][rg] = 0.f;  // read by this thread only: clean for the row block after next
+                            if (planes == 2) sv += sm.red_sh[par][ln + 2][rg], sm.red_sh[par][ln + 2][rg] = 0.f;
                             v = as_stored(v, y) + sm.gate[tok] * as_stored(sv, y);
                         }
                         if (sm.failed_mask >> tok & 1u) v = qnan();
