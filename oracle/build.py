@@ -41,14 +41,14 @@ def build(reference=DEFAULT_REF, force=False):
         _run(["g++", "-std=c++17", "-O3", "-march=native", "-fopenmp", "-fPIC", "-shared", src, "-o", out])
     ref_dir = os.path.join(HERE, "_ref")
     out = os.path.join(ref_dir, "libstrix_formats_ref.so")
-    fmts = [os.path.join(reference, "formats", f + ".cpp") for f in ("q4", "q5", "q6", "q8", "q4_from_q8")]
+    fmts = [os.path.join(reference, "formats", f + ".cpp") for f in ("q4", "q5", "q6", "q8", "q4_from_q8", "strixw")]
     if all(os.path.exists(f) for f in fmts):
-        shim = os.path.join(HERE, "ref_shim.cpp")
-        if force or _stale(out, fmts + [shim]):
+        shims = [os.path.join(HERE, "ref_shim.cpp"), os.path.join(HERE, "ref_strixw_shim.cpp")]
+        if force or _stale(out, fmts + shims):
             os.makedirs(ref_dir, exist_ok=True)
             # The reference's own sources, compiled where they lie: no -march/-mfma (keeps q*s+m unfused), C++20.
             _run(["g++", "-std=c++20", "-O2", "-ffp-contract=off", "-Wno-unknown-pragmas", "-pthread", "-fPIC",
-                  "-shared", "-I", reference] + fmts + [shim, "-o", out])
+                  "-shared", "-I", reference] + fmts + shims + ["-o", out])
     elif not os.path.exists(out):
         print("oracle/build.py: reference tree not mounted at %s and no prebuilt oracle/_ref - the reference-"
               "quantizer checks will be skipped" % reference, file=sys.stderr)

@@ -71,7 +71,6 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], 
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 __device__ __forceinline__ void named_sync(int id, int threads) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory"); }
-__device__ __forceinline__ void named_arrive(int id, int threads) { asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(threads) : "memory"); }
 __device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t mask, uint32_t orv) {
     uint32_t r;
     asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(a), "r"(mask), "r"(orv));  // (a & mask) | orv
@@ -114,7 +113,6 @@ struct Smem {
     float red_sh[2][32][8];      // phase 3: the separate shared expert's tile, kept apart for its own rounding
     float rpart[CW][kMaxTok];  // phase 1: half-row partial logits
     int leaders_before[CW + 2];
-    int gu_done[CW];             // per gate/up team: tiles whose partial sums the leader has read
     int n_groups, col_max, abort_flag;
     // phase 3 work list: a group's tokens in runs of at most kDnCols, so that a stage holds few h records and every warp
     // gets a stage (a wide group's weights are fetched once per run)
@@ -631,7 +629,6 @@ __global__ void __launch_bounds__(kThreads, 1) decode_fused_kernel(const __grid_
     float *xf = reinterpret_cast<float *>(stage_base);  // phases 0-1: x as FP32 [M][d], where the stages will be
 
     if (tid == 0) sm.abort_flag = 0, sm.failed_mask = 0, sm.n_groups = 0, sm.col_max = 1;
-    if (tid < CW) sm.gu_done[tid] = 0;
     stamp(p.sync, 0);
 
     // Phase 0: x -> FP32 copy, permuted planes, per-plane chunk sums.
@@ -826,56 +823,28 @@ __global__ void __launch_bounds__(kThreads, 1) decode_fused_kernel(const __grid_
                     __syncwarp();      // every lane is done with the stage
                     issue(n + D);      // refill it while the tile is finished
                 }
-                // The team's slices meet in the tile's leader - the leadership rotates (warp n % nk of the team leads the team's
-                // n-th tile) so that the SwiGLU epilogue is spread over the team. The others leave their partial sums and only
-                // ARRIVE at the tile's barrier; the leader waits on it, adds the slices in slice order and runs the epilogue while
-                // the others are already in the next tile. red[par] is reused two tiles later: done[team] counts the tiles whose
-                // partials the leader has read.
-                const int par = n & 1, lead = nk > 1 ? n % nk : 0;
+                // the team's slices meet in its leader (h == 0): ordered sum, then the SwiGLU, lane-local
+                const int par = n & 1;
                 if (nk > 1) {
-                    const int bar_id = 1 + 2 * team + par;
-                    // tile n - 2 used the same barrier and the same red[par]: its leader must have read its partials (which it does
-                    // after passing that barrier) before anyone touches either again
-                    if (lane == 0 && n >= 2) {
-                        volatile int *done = &sm.gu_done[team];
-                        uint32_t spins = 0;
-                        while (*done < n - 1 && !*(volatile int *)&sm.abort_flag)
-                            if (++spins > kSpinLimit) sm.abort_flag = 0x107;
-                    }
-                    __syncwarp();
-                    if (h != lead) {
+                    if (h != 0) {
                         float4 *dst = reinterpret_cast<float4 *>(&sm.red[par][cw][lane][0]);
                         dst[0] = make_float4(tot[0][0], tot[0][1], tot[0][2], tot[0][3]);
                         if (np == 2) dst[1] = make_float4(tot[1][0], tot[1][1], tot[1][2], tot[1][3]);
-                        __syncwarp();
-                        named_arrive(bar_id, nk * 32);
-                    } else {
-                        named_sync(bar_id, nk * 32);
-                        float sum[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-                        for (int w = 0; w < nk; ++w) {  // slice order, whoever leads
-                            if (w == h) {
-#pragma unroll
-                                for (int i = 0; i < 4; ++i) sum[0][i] += tot[0][i], sum[1][i] += tot[1][i];
-                            } else {
-                                const float4 *o = reinterpret_cast<const float4 *>(&sm.red[par][cw - h + w][lane][0]);
-                                const float4 o0 = o[0];
-                                sum[0][0] += o0.x, sum[0][1] += o0.y, sum[0][2] += o0.z, sum[0][3] += o0.w;
-                                if (np == 2) {
-                                    const float4 o1 = o[1];
-                                    sum[1][0] += o1.x, sum[1][1] += o1.y, sum[1][2] += o1.z, sum[1][3] += o1.w;
-                                }
+                    }
+                    named_sync(1 + team, nk * 32);
+                    if (h == 0) {
+                        for (int w = 1; w < nk; ++w) {
+                            const float4 *o = reinterpret_cast<const float4 *>(&sm.red[par][cw + w][lane][0]);
+                            const float4 o0 = o[0];
+                            tot[0][0] += o0.x, tot[0][1] += o0.y, tot[0][2] += o0.z, tot[0][3] += o0.w;
+                            if (np == 2) {
+                                const float4 o1 = o[1];
+                                tot[1][0] += o1.x, tot[1][1] += o1.y, tot[1][2] += o1.z, tot[1][3] += o1.w;
                             }
-                        }
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) tot[0][i] = sum[0][i], tot[1][i] = sum[1][i];
-                        __syncwarp();
-                        if (lane == 0) {
-                            __threadfence_block();
-                            *(volatile int *)&sm.gu_done[team] = n + 1;
                         }
                     }
                 }
-                if (h == lead && !sm.abort_flag) {
+                if (h == 0 && !sm.abort_flag) {
                     T *hh = static_cast<T *>(p.hh);
                     for (int ps = 0; ps < np; ++ps) {
                         // FP32 activations: the two planes of a token sit in lanes c and c ^ 2
