@@ -76,6 +76,9 @@ int strix_dequantize(int bits, const uint8_t *q, const uint16_t *scale, const ui
                      int64_t G, float *w);
 /* strixite formats/q4.hpp:31-32 check_q4 (and q5/q6/q8) on array sizes given in bytes / entries. */
 int strix_check_qweight(int bits, int64_t N, int64_t K, int64_t G, size_t q_bytes, size_t n_scale, size_t n_min);
+/* strixite formats/strixw.hpp:59 strix_hash64: the 64-bit hash of a byte range that strixw weight files carry for their
+ * header, index and every tensor component. Host memory. */
+uint64_t strix_hash64(const void *data, size_t n);
 /* strixite formats/q4.hpp:22-23, q5.hpp:31, q6.hpp:31: packed bytes of one row. */
 int64_t strix_row_bytes(int bits, int64_t K);
 /* The same quantizer on the device (w, q, scale, minv device arrays): bit-identical to strix_quantize. A non-finite

@@ -83,6 +83,7 @@ SIGNATURES = {
     "strix_linear_qmix_experts_gather_grouped": [_vp, _qm, _vp, _sz, _i64, _i64, _vp, _int, _int, _vp],
     "strix_linear_qmix_experts_combine_grouped": [_vp, _qm, _vp, _vp, _vp, _sz, _vp, _i64, _i64, _vp, _int, _int, _vp],
     "strix_moe_combine_reduce": [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _int, _vp],
+    "strix_hash64": [_vp, _sz],
     "strix_umma_abort_count": [],
     "strix_umma_wait_cycles": [_vp, _int],
     "strix_last_error": [],
@@ -90,6 +91,7 @@ SIGNATURES = {
 }
 _RESTYPES = {
     "strix_row_bytes": _i64,
+    "strix_hash64": C.c_uint64,
     "strix_umma_abort_count": C.c_uint,
     "strix_umma_wait_cycles": None,
     "strix_moe_route_workspace_bytes": _sz,

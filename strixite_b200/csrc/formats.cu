@@ -138,6 +138,40 @@ __global__ void __launch_bounds__(256) quantize_kernel(const float *w, int64_t N
 
 extern "C" {
 
+// strixite formats/strixw.hpp:59 strix_hash64 (formats/strixw.cpp:197-221): four interleaved multiply-xorshift lanes over
+// 8-byte little-endian words, 32 bytes per step; leftover whole words go to lanes 0, 1, 2; a last partial word is tagged
+// with its length; the lanes fold into one word with a final avalanche. Not a standard hash: the file format defines it.
+uint64_t strix_hash64(const void *data, size_t n) {
+    constexpr uint64_t k1 = 0x9e3779b97f4a7c15ull, k2 = 0xd6e8feb86659fd93ull;
+    auto mix = [](uint64_t h, uint64_t w) {
+        h ^= w * k1;
+        return (h ^ (h >> 31)) * k2;
+    };
+    const auto *p = static_cast<const uint8_t *>(data);
+    uint64_t lanes[4] = {n ^ k1, n ^ k2, ~(uint64_t)n ^ k1, ~(uint64_t)n ^ k2};
+    size_t i = 0;
+    for (; i + 32 <= n; i += 32)
+        for (int l = 0; l < 4; ++l) {
+            uint64_t w;
+            std::memcpy(&w, p + i + 8 * l, 8);
+            lanes[l] = mix(lanes[l], w);
+        }
+    for (int l = 0; i + 8 <= n; i += 8, ++l) {
+        uint64_t w;
+        std::memcpy(&w, p + i, 8);
+        lanes[l] = mix(lanes[l], w);
+    }
+    if (i < n) {
+        uint64_t w = 0;
+        std::memcpy(&w, p + i, n - i);
+        lanes[0] = mix(lanes[0], w ^ ((uint64_t)(n - i) << 56));
+    }
+    uint64_t r = mix(mix(mix(lanes[0], lanes[1]), lanes[2]), lanes[3]);
+    r ^= r >> 33;
+    r *= k1;
+    return r ^ (r >> 29);
+}
+
 int64_t strix_row_bytes(int bits, int64_t K) { return sb::row_bytes(bits, K); }
 
 int strix_check_qweight(int bits, int64_t N, int64_t K, int64_t G, size_t q_bytes, size_t n_scale, size_t n_min) {

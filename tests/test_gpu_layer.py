@@ -175,3 +175,30 @@ def test_prefill_tensor_core_path(act, router, G, shared, M):
     y1 = layer.forward(to_torch_act(x)).clone()
     y2 = layer.forward(to_torch_act(x))
     assert torch.equal(y1, y2)
+
+
+def test_layer_from_a_strixw_file(tmp_path):
+    # The weights of a layer written as a strixw file (router BF16 [E + 1, d] with the shared gate as row E, the expert stacks
+    # with the shared expert as expert E - the reference's merged layout, formats/merge_plan.cpp:29-42), read back through the
+    # file loaders: the layer built from the file gives the bits of the layer built from the arrays.
+    import strixite_b200 as sb
+    from strixite_b200 import strixw as SW
+
+    d, I, E, k, M = 512, 256, 12, 3, 7
+    L = make_layer(700, d=d, I=I, E=E, k=k, G=64, router="bf16", shared="stacked")
+    gu, dn = L["gate_up"], L["down"]
+    ts = [SW.Tensor("layers.0.moe.router", SW.BF16, [E + 1, d]),
+          SW.Tensor("layers.0.moe.experts.gate_up", SW.Q4_ROW, [(E + 1) * 2 * I, d], 64, E + 1),
+          SW.Tensor("layers.0.moe.experts.down", SW.Q4_ROW, [(E + 1) * d, I], 64, E + 1)]
+    data = {(ts[0].name, SW.DATA): L["router"],
+            (ts[1].name, SW.Q): gu.q, (ts[1].name, SW.SCALE): gu.scale, (ts[1].name, SW.MIN): gu.minv,
+            (ts[2].name, SW.Q): dn.q, (ts[2].name, SW.SCALE): dn.scale, (ts[2].name, SW.MIN): dn.minv}
+    path = str(tmp_path / "layer.strixw")
+    SW.write(path, {"model": "test"}, ts, data)
+    f = SW.StrixwFile(path)
+    f.verify_hashes()
+    assert f.get(ts[1].name).experts == E + 1
+    from_file = sb.MoeLayer(d, I, E, k, oracle.F32, f.dense(ts[0].name), f.qweight(ts[1].name), f.qweight(ts[2].name), shared="stacked", max_tokens=8)
+    direct = gpu_layer(L, oracle.F32, 8)
+    x = to_torch_act(randn_act(np.random.default_rng(701), (M, d), oracle.F32))
+    assert torch.equal(from_file.forward(x), direct.forward(x))
