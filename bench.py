@@ -346,7 +346,7 @@ def run_ep(args, cfg, rank, world, local, device, dist, barrier, line, P):
     torch.cuda.empty_cache()
     # capacity: with Zipf routing the hot rank receives several times the mean; 3x the mean plus the shared slots, checked below
     cap = min(T * (k + 1), 3 * T * k // world + Tl + 4096)
-    layer = EP.cuda_layer(d, I, E, k, K.Act.BF16, rw, bias, gu_l, dn_l, world, rank, max_local_tokens=Tl, capacity=cap)
+    layer = EP.cuda_layer(d, I, E, k, K.Act.BF16, rw, bias, gu_l, dn_l, world, rank, max_local_tokens=Tl, capacity=cap, dedup=not args.ep_exact)
     xs = []
     for r in range(cfg["ring"]):
         g.manual_seed(9000 + 17 * r)
@@ -392,7 +392,7 @@ def run_ep(args, cfg, rank, world, local, device, dist, barrier, line, P):
     fl = 2.0 * T * (k + 1) * 3 * I * d + 2.0 * T * (E + 1) * d
     step_s = ms * 1e-3 / args.steps
     line["scaling"] = "strong"
-    line["config"].update(parallelism="expert parallel x%d (experts e -> rank e / %d, tokens split evenly, shared expert replicated)" % (world, E // world),
+    line["config"].update(parallelism="expert parallel x%d (experts e -> rank e / %d, tokens split evenly, shared expert replicated; %s)" % (world, E // world, "one row per slot" if args.ep_exact else "one row per (token, rank), summed on the expert rank"),
                           router_bias="Zipf(1.1)", tokens_per_step=T, l2="two token sets alternate; every step streams far more than the 126 MB L2")
     line.update(value=T / step_s, ms_per_step=ms / args.steps, clocks=clocks)
     line["e2e"] = dict(value=T * ke / float(dt.item()), unit="tokens/s", h2d_bytes_per_step=int(xh[0].numel() * 2 * world), d2h_bytes_per_step=int(yh.numel() * 2 * world),
@@ -420,6 +420,7 @@ def main():
     ap.add_argument("--ring", type=int, default=0, help="override the number of independent (weights, tokens) pairs cycled (a small ring keeps a profiler capture small)")
     ap.add_argument("--tensor-min-tokens", type=int, default=0, help="with --math 2: run forwards of at least this many tokens on the tensor-core path")
     ap.add_argument("--math", type=int, default=-1, choices=[-1, 0, 1, 2], help="override the workload's MoeMath (0 = FP32 kernels, 1/2 = tensor cores)")
+    ap.add_argument("--ep-exact", action="store_true", help="expert parallel: one row per slot both ways (bit-identical to one GPU) instead of one per (token, rank)")
     ap.add_argument("--decode-impl", type=int, default=0, choices=[0, 1], help="forwards of <= 8 tokens: 0 = the fused kernel, 1 = the per-function kernels")
     args = ap.parse_args()
     cfg = dict(WORKLOADS[args.workload])

@@ -263,13 +263,15 @@ int strix_moe_layer_forward_host(strix_moe_layer *layer, const void *x_host, int
 /* x[M, d] += MoE_l(x) for l = 0 .. n_layers - 1 (residual_add between layers); tmp [M, d] is scratch. */
 int strix_moe_stack_forward(strix_moe_layer *const *layers, int64_t n_layers, void *x, int64_t M, void *tmp, void *stream);
 /* The expert half of the layer for expert-parallel runs, one call per batch of routed slots that arrived on this
- * device: rows[n, d] (the layer's activation dtype) holds one activation row per slot, ids[n] the slot's expert in THIS
- * layer's stacks (0 .. Estack - 1); partial[i, :] = W_down[ids[i]] * SwiGLU(W_gate_up[ids[i]] * rows[i]) in FP32, without
- * the routing coefficient. Groups the slots by expert and runs the tensor-core kernels; needs a layer created with
- * math != STRIX_MATH_F32 over uniform 4-bit stacks, and n <= max_tokens * (k + shared). Rows with an invalid id raise
- * the expert error words and are left unwritten. No counterpart in the reference (which has no expert parallelism). */
-int strix_moe_layer_experts_partial(strix_moe_layer *layer, const void *rows, const int32_t *ids, int64_t n, float *partial,
-                                    void *stream);
+ * device: ids[n] is each slot's expert in THIS layer's stacks (0 .. Estack - 1) and its activation row is
+ * rows[row_index[i], :] (the layer's activation dtype), or rows[i, :] when row_index is NULL - with row_index a token
+ * routed to several local experts is sent once. partial[i, :] = W_down[ids[i]] * SwiGLU(W_gate_up[ids[i]] * row) in FP32,
+ * without the routing coefficient. Groups the slots by expert and runs the tensor-core kernels; needs a layer created
+ * with math != STRIX_MATH_F32 over uniform 4-bit stacks, and n <= max_tokens * (k + shared). Slots with an invalid id
+ * raise the expert error words and are left unwritten. No counterpart in the reference (which has no expert
+ * parallelism). */
+int strix_moe_layer_experts_partial(strix_moe_layer *layer, const void *rows, const int32_t *row_index, const int32_t *ids,
+                                    int64_t n, float *partial, void *stream);
 /* The ordered weighted sum of the reference's combine (kernels/moe_grouped.hpp:60-62, second half): y[m, :] = sum over a
  * ascending of coef[m, a] * partial[m * A + a, :], one rounding; a token with an id outside [0, E) gets a NaN row.
  * pos (optional, [M * A]): slot (m, a) is row pos[m * A + a] of partial instead of row m * A + a - partial rows that

@@ -288,7 +288,7 @@ int strix_moe_layer_forward(strix_moe_layer *L, const void *x, int64_t M, void *
         // many tokens on the tensor cores: bucket-ordered F16 activations, gate/up with SwiGLU in its epilogue, down into
         // FP32 partials, then the ordered reduction of the reference's combine
         SB_TRY(strix_moe_group_routes(L->ids, M, A, L->Estack, L->group_ws, L->group_ws_bytes, expert_err, stream));
-        SB_TRY(sb::prefill_experts(L->prefill, x, act, static_cast<const int32_t *>(L->group_ws), M, A, L->partial, st));
+        SB_TRY(sb::prefill_experts(L->prefill, x, nullptr, act, static_cast<const int32_t *>(L->group_ws), M, A, L->partial, st));
         SB_TRY(sb::combine_reduce(fn, L->partial, L->ids, L->coef, M, A, L->Estack, d.d, y, act, st));
     } else if (M >= d.grouped_min_tokens) {
         SB_TRY(strix_moe_group_routes(L->ids, M, A, L->Estack, L->group_ws, L->group_ws_bytes, expert_err, stream));
@@ -324,14 +324,15 @@ int strix_moe_layer_forward(strix_moe_layer *L, const void *x, int64_t M, void *
     return 0;
 }
 
-int strix_moe_layer_experts_partial(strix_moe_layer *L, const void *rows, const int32_t *ids, int64_t n, float *partial, void *stream) {
+int strix_moe_layer_experts_partial(strix_moe_layer *L, const void *rows, const int32_t *row_index, const int32_t *ids, int64_t n, float *partial,
+                                    void *stream) {
     const char *fn = "moe_layer_experts_partial";
     SB_CHECK(L != nullptr && rows != nullptr && ids != nullptr && partial != nullptr, fn, ": null pointer");
     SB_CHECK(L->prefill != nullptr, fn, ": the layer has no tensor-core plan (needs math != F32, uniform 4-bit stacks, d % 256 == 0, I % 128 == 0 and max_tokens >= tensor_min_tokens)");
     SB_CHECK(n >= 1 && n <= L->d.max_tokens * L->A, fn, ": ", n, " rows, expected 1..", L->d.max_tokens * L->A);
     auto st = static_cast<cudaStream_t>(stream);
     SB_TRY(strix_moe_group_routes(ids, n, 1, L->Estack, L->group_ws, L->group_ws_bytes, L->err + 3, stream));
-    SB_TRY(sb::prefill_experts(L->prefill, rows, L->d.act, static_cast<const int32_t *>(L->group_ws), n, 1, partial, st));
+    SB_TRY(sb::prefill_experts(L->prefill, rows, row_index, L->d.act, static_cast<const int32_t *>(L->group_ws), n, 1, partial, st));
     return 0;
 }
 

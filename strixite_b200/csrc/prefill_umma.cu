@@ -119,13 +119,14 @@ __global__ void __launch_bounds__(1024) tiles_kernel(const int32_t *ws, int32_t 
 
 // One warp per sorted position p < offsets[E] (the slots with a valid expert).
 template <typename T>
-__global__ void __launch_bounds__(256) pregather_kernel(const T *x, const int32_t *ws, int64_t A, int64_t K, uint16_t *xg) {
+__global__ void __launch_bounds__(256) pregather_kernel(const T *x, const int32_t *row_index, const int32_t *ws, int64_t A, int64_t K, uint16_t *xg) {
     const int32_t S = ws[1], E = ws[2];
     const RouteTables rt = route_tables(ws, S, E);
     const int32_t total = rt.offsets[E];
     const int lane = threadIdx.x & 31;
     for (int64_t p = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5); p < total; p += (int64_t)gridDim.x * 8) {
-        const T *src = x + (int64_t)(rt.slots[p] / A) * K;
+        const int32_t slot = rt.slots[p];
+        const T *src = x + (int64_t)(row_index != nullptr ? row_index[slot] : slot / A) * K;  // row_index: slot -> activation row
         uint4 *dst = reinterpret_cast<uint4 *>(xg + p * K);
         for (int c = lane; c < K / 8; c += 32) dst[c] = act_chunk(src + c * 8);
     }
@@ -642,7 +643,8 @@ bool dense_bf16_ok(const void *x, const void *w, int64_t M, int64_t N, int64_t K
            reinterpret_cast<uintptr_t>(w) % 16 == 0;
 }
 
-int prefill_experts(PrefillPlan *p, const void *x, int act, const int32_t *ws, int64_t M, int64_t A, float *partial, cudaStream_t st) {
+int prefill_experts(PrefillPlan *p, const void *x, const int32_t *row_index, int act, const int32_t *ws, int64_t M, int64_t A, float *partial,
+                    cudaStream_t st) {
     const char *fn = "moe_layer_forward (tensor-core experts)";
     // a handful of tokens (decode, verify): tiles of 32 slots and four issuing warps; many tokens: tiles of 96 slots
     const bool small = M * A <= kSmallSlots;
@@ -650,8 +652,8 @@ int prefill_experts(PrefillPlan *p, const void *x, int act, const int32_t *ws, i
     SB_LAUNCH_OK(fn, ": tiles");
     SB_CHECK(M * A <= p->max_tokens * p->A, fn, ": ", M * A, " slots exceed the layer's ", p->max_tokens * p->A);
     const unsigned gblocks = (unsigned)std::min<int64_t>((M * A + 7) / 8, 148 * 16);
-    if (act == kF32) pregather_kernel<float><<<gblocks, 256, 0, st>>>((const float *)x, ws, A, p->d, p->xg);
-    else pregather_kernel<uint16_t><<<gblocks, 256, 0, st>>>((const uint16_t *)x, ws, A, p->d, p->xg);
+    if (act == kF32) pregather_kernel<float><<<gblocks, 256, 0, st>>>((const float *)x, row_index, ws, A, p->d, p->xg);
+    else pregather_kernel<uint16_t><<<gblocks, 256, 0, st>>>((const uint16_t *)x, row_index, ws, A, p->d, p->xg);
     SB_LAUNCH_OK(fn, ": gather");
     FfnArgs a{};
     a.ws = ws, a.tiles = p->tiles;

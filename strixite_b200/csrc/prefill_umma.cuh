@@ -19,8 +19,9 @@ bool prefill_has_dense_router(const PrefillPlan *p);
 int prefill_router_logits(PrefillPlan *p, const void *x, int64_t M, float *logits, const float *bias, int64_t n_bias, cudaStream_t st);
 // Tiles -> bucket-ordered F16 activations -> gate/up + SwiGLU -> down: FP32 partial[slot, d] for every slot with a
 // valid expert. `ws` is the grouping workspace of moe_group_routes for (M, A, Estack).
-// x holds one row per token; slot s reads row s / A.
-int prefill_experts(PrefillPlan *p, const void *x, int act, const int32_t *ws, int64_t M, int64_t A, float *partial, cudaStream_t st);
+// Slot s reads activation row row_index[s], or s / A (one row per token) when row_index is null.
+int prefill_experts(PrefillPlan *p, const void *x, const int32_t *row_index, int act, const int32_t *ws, int64_t M, int64_t A, float *partial,
+                    cudaStream_t st);
 // y[M, N] (FP32) = x[M, K] (BF16) * w[N, K]^T (BF16) + bias[n < n_bias] on the tensor cores; dense_bf16_ok says whether the
 // shape and alignment qualify (M >= 64, K % 64 == 0, 16-byte aligned pointers).
 bool dense_bf16_ok(const void *x, const void *w, int64_t M, int64_t N, int64_t K);

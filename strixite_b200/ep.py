@@ -15,6 +15,12 @@ counterpart there; its contract is "the same output as the single-device layer":
 A slot's partial row depends on nothing but its own row and expert, and the final sum runs in slot order on the home
 rank, so the result does not depend on the number of ranks.
 
+That is the exact mode (dedup=False). The default mode (dedup=True) moves less: a token's row goes ONCE to every rank that
+owns one of its experts (with its slots' expert ids and coefficients), the expert rank sums coef * partial over the
+token's slots it served (ascending slot order) and returns ONE FP32 row per (token, rank), and the home rank adds those
+in ascending rank order. Same arithmetic, another association: results are reproducible for a given number of ranks and
+agree with the single-device layer to FP32 rounding, not bit for bit.
+
 The exchange plumbing is torch (index_select / argsort / all_to_all_single on whatever device the tensors live on);
 the three compute steps are callables, by default the CUDA library's. Tests drive the same plumbing over gloo on CPU
 tensors with the oracle's functions plugged in.
@@ -24,16 +30,20 @@ import torch.distributed as dist
 
 
 class ExpertParallelMoe:
-    def __init__(self, E, k, world, rank, route_fn, experts_fn, reduce_fn, group=None, shared=True):
+    def __init__(self, E, k, world, rank, route_fn, experts_fn, reduce_fn, group=None, shared=True, dedup=True):
         """E routed experts (E % world == 0), top-k; `shared`: a stacked shared expert with id E rides slot k.
         route_fn(x) -> (ids int32 [T, A], coef float32 [T, A]);  experts_fn(rows [n, d], local_ids int32 [n]) -> float32 [n, d];
-        reduce_fn(partial float32 [T * A, d], pos int64 [T * A], ids, coef) -> y [T, d], slot (t, a) being row pos[t * A + a]."""
+        reduce_fn(partial float32 [R, d], pos int64 [T, W], ids int32 [T, W], coef float32 [T, W], out_dtype) -> [T, d]:
+        y[t] = sum over w ascending of coef[t, w] * partial[pos[t, w]] (ids only say valid / invalid), rounded once to
+        out_dtype (None = the activation dtype). With dedup, experts_fn(rows, local_ids, row_index int32 [n]) reads slot
+        i's activation from rows[row_index[i]]."""
         if E % world != 0:
             raise ValueError("ExpertParallelMoe: %d experts do not divide over %d ranks" % (E, world))
         self.E, self.k, self.world, self.rank, self.group = E, k, world, rank, group
         self.El = E // world
         self.A = k + (1 if shared else 0)
         self.route_fn, self.experts_fn, self.reduce_fn = route_fn, experts_fn, reduce_fn
+        self.dedup = dedup
         self.last = {}
 
     def plan(self, ids):
@@ -52,7 +62,6 @@ class ExpertParallelMoe:
     def forward(self, x, timings=None):
         """y [T, d] for this rank's tokens x [T, d]. timings: an optional dict that receives the milliseconds of each phase
         (CUDA events; adds a synchronization at the end)."""
-        T, d = x.shape
         marks = []
 
         def mark(name):
@@ -62,15 +71,28 @@ class ExpertParallelMoe:
                 marks.append((name, ev))
 
         mark("start")
+        y = self._forward_dedup(x, mark) if self.dedup else self._forward_exact(x, mark)
+        if marks:
+            torch.cuda.synchronize()
+            for (_, a), (name, b) in zip(marks[:-1], marks[1:]):
+                timings[name] = timings.get(name, 0.0) + a.elapsed_time(b)
+        return y
+
+    def _exchange_counts(self, counts):
+        """counts int64 [world, c] per destination -> what every source sends here, as host lists (split sizes are host ints)."""
+        recv = torch.empty_like(counts)
+        dist.all_to_all_single(recv, counts, group=self.group)
+        return counts.tolist(), recv.tolist()
+
+    def _forward_exact(self, x, mark):
+        T, d = x.shape
         ids, coef = self.route_fn(x)
         mark("route")
         order, send_ids, counts = self.plan(ids)
         send_rows = x.index_select(0, torch.div(order, self.A, rounding_mode="floor"))
         mark("plan+gather")
-        # counts both ways (host integers: all_to_all_single wants split sizes)
-        recv_counts = torch.empty_like(counts)
-        dist.all_to_all_single(recv_counts, counts, group=self.group)
-        out_splits, in_splits = counts.tolist(), recv_counts.tolist()
+        out_c, in_c = self._exchange_counts(counts.reshape(-1, 1))
+        out_splits, in_splits = [c[0] for c in out_c], [c[0] for c in in_c]
         mark("counts")
         n_recv = int(sum(in_splits))
         recv_rows = x.new_empty((n_recv, d))
@@ -78,7 +100,7 @@ class ExpertParallelMoe:
         dist.all_to_all_single(recv_rows, send_rows, in_splits, out_splits, group=self.group)
         dist.all_to_all_single(recv_ids, send_ids, in_splits, out_splits, group=self.group)
         mark("dispatch")
-        partial = self.experts_fn(recv_rows, recv_ids) if n_recv else torch.empty((0, d), dtype=torch.float32, device=x.device)
+        partial = self.experts_fn(recv_rows, recv_ids, None) if n_recv else torch.empty((0, d), dtype=torch.float32, device=x.device)
         mark("experts")
         back = torch.empty((T * self.A, d), dtype=torch.float32, device=x.device)
         dist.all_to_all_single(back, partial, out_splits, in_splits, group=self.group)
@@ -86,17 +108,89 @@ class ExpertParallelMoe:
         pos = torch.empty_like(order)
         pos[order] = torch.arange(order.numel(), device=order.device)  # slot t * A + a came back as row pos[t * A + a]
         self.last = dict(ids=ids, coef=coef, sent=out_splits, received=in_splits)
-        y = self.reduce_fn(back, pos, ids, coef)
+        y = self.reduce_fn(back, pos.reshape(T, self.A), ids, coef, None)
         mark("reduce")
-        if marks:
-            torch.cuda.synchronize()
-            for (_, a), (name, b) in zip(marks[:-1], marks[1:]):
-                timings[name] = timings.get(name, 0.0) + a.elapsed_time(b)
+        return y
+
+    def _forward_dedup(self, x, mark):
+        T, d = x.shape
+        dev = x.device
+        W, A = self.world, self.A
+        ids, coef = self.route_fn(x)
+        mark("route")
+        order, send_ids, slot_counts = self.plan(ids)  # slots by destination, (token, slot) order inside a destination
+        S = order.numel()
+        tok = torch.div(order, A, rounding_mode="floor")
+        dest = torch.repeat_interleave(torch.arange(W, device=dev), slot_counts, output_size=S)
+        # pairs (destination, token): a new pair starts where either changes along the sorted slots
+        new_pair = torch.ones(S, dtype=torch.bool, device=dev)
+        new_pair[1:] = (tok[1:] != tok[:-1]) | (dest[1:] != dest[:-1])
+        pair_of_slot = torch.cumsum(new_pair.to(torch.int64), 0) - 1          # global pair index of every sorted slot
+        first = torch.nonzero(new_pair).reshape(-1)                           # first sorted slot of every pair
+        pair_tok, pair_dest = tok[first], dest[first]
+        pair_counts = torch.bincount(pair_dest, minlength=W)
+        pair_start = torch.cumsum(pair_counts, 0) - pair_counts               # first pair of every destination
+        send_rows = x.index_select(0, pair_tok)
+        send_rel = (pair_of_slot - pair_start[dest]).to(torch.int32)           # the slot's row inside its destination's block
+        send_coef = coef.reshape(-1)[order]
+        mark("plan+gather")
+        out_c, in_c = self._exchange_counts(torch.stack([slot_counts, pair_counts], 1))
+        out_slots, out_pairs = [c[0] for c in out_c], [c[1] for c in out_c]
+        in_slots, in_pairs = [c[0] for c in in_c], [c[1] for c in in_c]
+        mark("counts")
+        n_slots, n_pairs = int(sum(in_slots)), int(sum(in_pairs))
+        recv_rows = x.new_empty((n_pairs, d))
+        recv_ids = send_ids.new_empty((n_slots,))
+        recv_rel = send_rel.new_empty((n_slots,))
+        recv_coef = send_coef.new_empty((n_slots,))
+        dist.all_to_all_single(recv_rows, send_rows, in_pairs, out_pairs, group=self.group)
+        dist.all_to_all_single(recv_ids, send_ids, in_slots, out_slots, group=self.group)
+        dist.all_to_all_single(recv_rel, send_rel, in_slots, out_slots, group=self.group)
+        dist.all_to_all_single(recv_coef, send_coef, in_slots, out_slots, group=self.group)
+        mark("dispatch")
+        # the slot's row among everything received: its source's first row + its row inside the source's block
+        in_slots_t, in_pairs_t = torch.tensor(in_slots, device=dev), torch.tensor(in_pairs, device=dev)
+        src = torch.repeat_interleave(torch.arange(W, device=dev), in_slots_t, output_size=n_slots)
+        row_index = (recv_rel.to(torch.int64) + (torch.cumsum(in_pairs_t, 0) - in_pairs_t)[src])
+        if n_slots:
+            partial = self.experts_fn(recv_rows, recv_ids, row_index.to(torch.int32))
+        else:
+            partial = torch.empty((0, d), dtype=torch.float32, device=dev)
+        mark("experts")
+        # expert-side sum per received row: its slots are consecutive (the source sorted them); a table [rows, k + 1] of slot
+        # positions, padded with coefficient 0 on a valid row, feeds the ordered weighted sum
+        if n_pairs:
+            start = torch.ones(n_slots, dtype=torch.bool, device=dev)
+            start[1:] = row_index[1:] != row_index[:-1]
+            first_slot = torch.nonzero(start).reshape(-1)                       # one per received row, in row order
+            rank_in_row = torch.arange(n_slots, device=dev) - first_slot[row_index]
+            pos_t = torch.zeros((n_pairs, A), dtype=torch.int64, device=dev)
+            coef_t = torch.zeros((n_pairs, A), dtype=torch.float32, device=dev)
+            ids_t = torch.zeros((n_pairs, A), dtype=torch.int32, device=dev)
+            pos_t[row_index, rank_in_row] = torch.arange(n_slots, device=dev)
+            coef_t[row_index, rank_in_row] = recv_coef
+            ids_t[row_index, rank_in_row] = torch.where(recv_ids < 0, recv_ids, torch.zeros_like(recv_ids))  # invalid ids poison the row
+            summed = self.reduce_fn(partial, pos_t, ids_t, coef_t, torch.float32)
+        else:
+            summed = torch.empty((0, d), dtype=torch.float32, device=dev)
+        mark("expert-side sum")
+        back = torch.empty((int(sum(out_pairs)), d), dtype=torch.float32, device=dev)
+        dist.all_to_all_single(back, summed, out_pairs, in_pairs, group=self.group)
+        mark("combine all-to-all")
+        # home: token t's rows, one per rank that served it, added in ascending rank order
+        pos_h = torch.zeros((T, W), dtype=torch.int64, device=dev)
+        coef_h = torch.zeros((T, W), dtype=torch.float32, device=dev)
+        pos_h[pair_tok, pair_dest] = torch.arange(pair_tok.numel(), device=dev)
+        coef_h[pair_tok, pair_dest] = 1.0
+        ids_h = torch.zeros((T, W), dtype=torch.int32, device=dev)
+        self.last = dict(ids=ids, coef=coef, sent=out_slots, received=in_slots, rows_sent=out_pairs, rows_received=in_pairs)
+        y = self.reduce_fn(back, pos_h, ids_h, coef_h, None)
+        mark("reduce")
         return y
 
 
 def cuda_layer(d, I, E, k, act, router_w, router_bias, gate_up_local, down_local, world, rank, max_local_tokens, capacity=None, group=None,
-               math=2):
+               math=2, dedup=True):
     """The expert-parallel layer on this rank's GPU. router_w: BF16 or FP32 [E + 1, d] (row E gates the shared expert),
     replicated. gate_up_local / down_local: this rank's E / world routed experts followed by the shared expert
     ([(E / world + 1) * 2I, d] and [(E / world + 1) * d, I], uniform 4-bit). capacity: the most slots this rank accepts in
@@ -126,16 +220,17 @@ def cuda_layer(d, I, E, k, act, router_w, router_bias, gate_up_local, down_local
         K.moe_router(logits, R, T, E, k, logits[:, E:], R, E, ids, coef, K.Act.F32, err)
         return ids, coef
 
-    def experts(rows, local_ids):
-        return shard.experts_partial(rows, local_ids)
+    def experts(rows, local_ids, row_index):
+        return shard.experts_partial(rows, local_ids, row_index=row_index)
 
-    def reduce(partial, pos, ids, coef):
-        T = ids.shape[0]
-        y = torch.empty((T, d), dtype=K._dtype(act), device=partial.device)
-        K.moe_combine_reduce(partial, ids, coef, T, A, E + 1, d, y, act, pos=pos)
+    def reduce(partial, pos, ids, coef, out_dtype):
+        T, Wd = ids.shape
+        out_act = K.Act.F32 if out_dtype == torch.float32 else act
+        y = torch.empty((T, d), dtype=K._dtype(out_act), device=partial.device)
+        K.moe_combine_reduce(partial, ids.contiguous(), coef.contiguous(), T, Wd, E + 1, d, y, out_act, pos=pos.contiguous())
         return y
 
-    ep = ExpertParallelMoe(E, k, world, rank, route, experts, reduce, group=group)
+    ep = ExpertParallelMoe(E, k, world, rank, route, experts, reduce, group=group, dedup=dedup)
     ep.shard = shard
     return ep
 

@@ -41,7 +41,7 @@ lib.strix_moe_layer_probe.argtypes = [C.c_void_p, C.c_char_p]
 lib.strix_moe_layer_probe.restype = C.c_void_p
 lib.strix_moe_layer_reset_errors.argtypes = [C.c_void_p, C.c_void_p]
 lib.strix_moe_layer_reset_errors.restype = C.c_int
-lib.strix_moe_layer_experts_partial.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p]
+lib.strix_moe_layer_experts_partial.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p]
 lib.strix_moe_layer_experts_partial.restype = C.c_int
 
 
@@ -109,12 +109,13 @@ class MoeLayer:
         call("strix_moe_layer_forward_host", self._h, x_host.ctypes.data_as(C.c_void_p), M, y_host.ctypes.data_as(C.c_void_p), K._s(stream))
         return y_host
 
-    def experts_partial(self, rows, ids, partial=None, stream=None):
-        """partial[i, :] = W_down[ids[i]] * SwiGLU(W_gate_up[ids[i]] * rows[i]) in FP32 for a batch of routed slots (one
-        activation row and one expert of this layer's stacks per slot): the expert half of an expert-parallel layer."""
-        n = rows.shape[0]
+    def experts_partial(self, rows, ids, partial=None, stream=None, row_index=None):
+        """partial[i, :] = W_down[ids[i]] * SwiGLU(W_gate_up[ids[i]] * row_i) in FP32 for a batch of routed slots: the expert
+        half of an expert-parallel layer. row_i = rows[row_index[i]] (int32 index), or rows[i] when row_index is None."""
+        n = ids.shape[0]
         partial = torch.empty((n, self.d), dtype=torch.float32, device=rows.device) if partial is None else partial
-        call("strix_moe_layer_experts_partial", self._h, K._p(rows), K._p(ids), n, K._p(partial), K._s(stream))
+        call("strix_moe_layer_experts_partial", self._h, K._p(rows), None if row_index is None else K._p(row_index), K._p(ids), n, K._p(partial),
+             K._s(stream))
         return partial
 
     def reset_errors(self, stream=None):

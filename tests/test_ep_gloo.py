@@ -34,7 +34,9 @@ def _oracle_callables(L, world, rank):
         ids, coef, _ = oracle.moe_router(logits, E, K_TOP, shared_col=E, shared_id=E)
         return torch.from_numpy(ids), torch.from_numpy(coef)
 
-    def experts(rows, local_ids):
+    def experts(rows, local_ids, row_index):
+        if row_index is not None:
+            rows = rows[row_index.to(torch.int64)]
         loc = local_ids.numpy()
         assert ((loc >= 0) & (loc <= El)).all()
         gid = np.where(loc == El, E, rank * El + loc).astype(np.int32).reshape(-1, 1)  # back to ids of the full stacks
@@ -42,20 +44,20 @@ def _oracle_callables(L, world, rank):
         y, _ = oracle.experts_combine(np.ascontiguousarray(h.reshape(-1, I)), L["down"], gid, np.ones_like(gid, dtype=np.float32))
         return torch.from_numpy(y)
 
-    def reduce(partial, pos, ids, coef):
-        p = partial.numpy()[pos.numpy()].astype(np.float64).reshape(ids.shape[0], ids.shape[1], -1)
+    def reduce(partial, pos, ids, coef, out_dtype):
+        p = partial.numpy()[pos.numpy().reshape(-1)].astype(np.float64).reshape(ids.shape[0], ids.shape[1], -1)
         return torch.from_numpy((coef.numpy().astype(np.float64)[:, :, None] * p).sum(axis=1).astype(np.float32))
 
     return route, experts, reduce
 
 
-def _worker(rank, world, port, out_dir):
+def _worker(rank, world, port, out_dir, dedup):
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
         L, x = _layer(), _tokens()
         lo, hi = rank * T // world, (rank + 1) * T // world  # uneven shares on purpose when T % world != 0
-        ep = ExpertParallelMoe(E, K_TOP, world, rank, *_oracle_callables(L, world, rank))
+        ep = ExpertParallelMoe(E, K_TOP, world, rank, *_oracle_callables(L, world, rank), dedup=dedup)
         y = ep.forward(torch.from_numpy(x[lo:hi].copy()))
         # plan properties: a permutation of the slots, destinations ascending, slot order kept inside a destination
         order, loc, counts = ep.plan(ep.last["ids"])
@@ -79,9 +81,10 @@ def _free_port():
         return s.getsockname()[1]
 
 
+@pytest.mark.parametrize("dedup", (False, True))
 @pytest.mark.parametrize("world", (1, 2))
-def test_expert_parallel_exchange_matches_single_process(world, tmp_path):
-    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+def test_expert_parallel_exchange_matches_single_process(world, dedup, tmp_path):
+    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path), dedup), nprocs=world, join=True)
     y = np.concatenate([np.load(tmp_path / ("y%d.npy" % r)) for r in range(world)])
     want, it = oracle.moe_layer(_tokens(), _layer())
     assert y.shape == want.shape
