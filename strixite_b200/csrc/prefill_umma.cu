@@ -3,30 +3,32 @@
 //   dense_umma_kernel   router logits[M, R] = x[M, d] * Wr[R, d]^T for BF16 activations and a BF16 router (products of
 //                       two BF16 values are exact in FP32, so this equals the FP32-FMA projection up to summation
 //                       order). Both operands arrive by TMA with the 128-byte swizzle; no thread touches them.
-//   tiles_kernel        the per-expert buckets of the grouping workspace cut into tiles of at most 128 routed slots.
-//   pregather_kernel    xg[p, :] = F16(x[token of sorted slot p, :]): the activations in bucket order, so that a tile's
-//                       tokens are 128 consecutive rows one TMA box can fetch.
+//   tiles_kernel        the per-expert buckets of the grouping workspace cut into tiles of at most 96 routed slots (32 in
+//                       the small shape).
+//   pregather_kernel    xg[p, :] = F16(x[row of sorted slot p, :]): the activations in bucket order, so that a tile's
+//                       tokens are consecutive rows one TMA box can fetch.
 //   ffn_umma_kernel<0>  hs[p, i] = SwiGLU(gate, up) with gate/up = W_gate_up[e] * xg[p]: one work item = one tile x 128
-//                       intermediate columns = two accumulators (128 gate rows and the matching 128 up rows), so that a
+//                       intermediate columns = two row halves (128 gate rows and the matching 128 up rows), so that a
 //                       thread of the epilogue holds gate and up of the same output.
 //   ffn_umma_kernel<1>  partial[slot, n] = W_down[e] * hs[p]: one work item = one tile x 256 output rows.
 //
-// One CTA per SM walks its work items (26 warps). Roles:
-//   warp 24     TMA producer: packed 4-bit codes (boxes of 128 rows x 64 bytes, 64-byte swizzle) into a 3-deep ring of
-//               raw stages, token tiles (128 rows x 64 F16, 128-byte swizzle) into a 4-deep ring.
-//   warps 0-15  dequantizers: thread = 64 codes of one weight row per raw stage -> F16 code * s + m (lop3
-//               "1024 + code", exact subtract, one F16 FMA) stored in the K-major 128-byte-swizzled layout the tensor
-//               core reads (3-deep ring of [A0 | A1]). Both operands keep each 8 K elements in the order
-//               0,4,1,5,2,6,3,7 (what the nibble unpack produces); xg and hs are written in that order.
-//   warps 25-26 one per accumulator: issue tcgen05.mma (cta_group::1, kind::f16, FP32 accumulation, A from tensor memory);
-//               tcgen05.commit frees operand stages and publishes finished accumulators. Warp 25 allocates all 512
+// One CTA per SM walks its work items. Roles (wide shape; the small shape has 4 epilogue and 4 issuing warps):
+//   warps 0-15  dequantizers: thread = 64 codes of one weight row per raw stage -> F16 code * s + m (lop3 "1024 + code",
+//               exact subtract, one F16 FMA), stored with tcgen05.st into an A stage in TENSOR MEMORY (lane = weight row,
+//               32 columns = 64 F16): the MMA takes A from tensor memory and only B from shared memory. Both operands keep
+//               each 8 K elements in the order 0,4,1,5,2,6,3,7 (what the nibble unpack produces); xg and hs are written
+//               in that order.
+//   warps 16-23 epilogue: tcgen05.ld (lane = weight row, column = routed slot) of one accumulator buffer while the next
+//               work item accumulates in the other.
+//   warp 24     TMA producer: packed 4-bit codes (boxes of 128 rows x 64 bytes, 64-byte swizzle) into a 6-deep ring of raw
+//               stages, token tiles (96 rows x 64 F16, 128-byte swizzle) into a 6-deep ring.
+//   warps 25-26 one per accumulator: issue tcgen05.mma (cta_group::1, kind::f16, FP32 accumulation) and one tcgen05.commit
+//               per K block, under which the probe of the next K block's barrier is issued. Warp 25 allocates all 512
 //               tensor-memory columns (two buffers of two 96-column accumulators + two A stages of 64 columns).
-//   warps 16-23 epilogue: tcgen05.ld (lane = weight row, column = routed slot) of one buffer while the next work item
-//               accumulates in the other.
 // Every mbarrier wait is bounded: on expiry the CTA raises the abort counter, frees its tensor memory and returns.
-// What bounds it: shared-memory bandwidth. Per K block the tensor core reads 32 KB of A and twice the token tile, the
-// dequantizers write those 32 KB and read 16 KB of codes, TMA writes 32 KB: ~130 KB at 128 bytes per clock is about twice
-// the MMA time at 80 tokens per expert.
+// What bounds it (measured): a tcgen05.mma occupies its issuing thread ~100 cycles for any N <= 128 and the tensor-memory
+// instruction path takes about one tcgen05 operation (mma, commit, st, ld) per ~45 cycles per SM; with ~80 slots per
+// expert a K block of 256 rows is 8 MMAs + 2 commits + 8 stores ~ 1000 cycles for ~300 cycles of tensor work.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
