@@ -435,6 +435,9 @@ def main():
     if args.warmup < 3:
         args.warmup = 3
 
+    # torchrun sets OMP_NUM_THREADS=1 for its workers; the CPU legs (rank 0 only) are meant to use every host core
+    os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
+
     import torch
 
     import oracle  # noqa: F401  (the CPU legs only)

@@ -494,13 +494,9 @@ __device__ void build_groups(const DecodeParams &p, Smem &sm, int tid) {
     }
     __syncthreads();
     if (tid < sm.n_groups) resolve_group(p, sm.groups[tid]);
-    if (tid == 0) {
-        int cm = 1;
-        for (int gi = 0; gi < sm.n_groups; ++gi) {
-            const int c = __popc(sm.groups[gi].mask);
-            cm = c > cm ? c : cm;
-        }
-        sm.col_max = cm < kDnCols ? cm : kDnCols;
+    if (tid < sm.n_groups) {  // the widest stage of phase 3 (col_max starts at 1)
+        const int c = __popc(sm.groups[tid].mask);
+        atomicMax(&sm.col_max, c < kDnCols ? c : kDnCols);
     }
     // phase 3 work list, in group order: thread gi owns group gi's runs; positions by a scan over the first 96 threads
     {

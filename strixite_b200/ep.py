@@ -140,13 +140,12 @@ class ExpertParallelMoe:
         mark("counts")
         n_slots, n_pairs = int(sum(in_slots)), int(sum(in_pairs))
         recv_rows = x.new_empty((n_pairs, d))
-        recv_ids = send_ids.new_empty((n_slots,))
-        recv_rel = send_rel.new_empty((n_slots,))
-        recv_coef = send_coef.new_empty((n_slots,))
+        # one message per slot: local expert id, row inside the destination's block, coefficient (bits)
+        send_meta = torch.stack([send_ids, send_rel, send_coef.view(torch.int32)], 1).contiguous()
+        recv_meta = send_meta.new_empty((n_slots, 3))
         dist.all_to_all_single(recv_rows, send_rows, in_pairs, out_pairs, group=self.group)
-        dist.all_to_all_single(recv_ids, send_ids, in_slots, out_slots, group=self.group)
-        dist.all_to_all_single(recv_rel, send_rel, in_slots, out_slots, group=self.group)
-        dist.all_to_all_single(recv_coef, send_coef, in_slots, out_slots, group=self.group)
+        dist.all_to_all_single(recv_meta, send_meta, in_slots, out_slots, group=self.group)
+        recv_ids, recv_rel, recv_coef = recv_meta[:, 0].contiguous(), recv_meta[:, 1], recv_meta[:, 2].contiguous().view(torch.float32)
         mark("dispatch")
         # the slot's row among everything received: its source's first row + its row inside the source's block
         in_slots_t, in_pairs_t = torch.tensor(in_slots, device=dev), torch.tensor(in_pairs, device=dev)
