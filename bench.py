@@ -421,10 +421,13 @@ def main():
     ap.add_argument("--tensor-min-tokens", type=int, default=0, help="with --math 2: run forwards of at least this many tokens on the tensor-core path")
     ap.add_argument("--math", type=int, default=-1, choices=[-1, 0, 1, 2], help="override the workload's MoeMath (0 = FP32 kernels, 1/2 = tensor cores)")
     ap.add_argument("--ep-exact", action="store_true", help="expert parallel: one row per slot both ways (bit-identical to one GPU) instead of one per (token, rank)")
+    ap.add_argument("--grouped-min", type=int, default=0, help="override the token count from which the grouped expert path runs (reference: 6)")
     ap.add_argument("--decode-impl", type=int, default=0, choices=[0, 1], help="forwards of <= 8 tokens: 0 = the fused kernel, 1 = the per-function kernels")
     args = ap.parse_args()
     cfg = dict(WORKLOADS[args.workload])
     cfg["decode_impl"] = args.decode_impl
+    if args.grouped_min > 0:
+        cfg["grouped_min"] = args.grouped_min
     cfg["tensor_min_tokens"] = args.tensor_min_tokens
     if args.math >= 0:
         cfg["math"] = args.math
