@@ -187,11 +187,13 @@ __global__ void __launch_bounds__(256)
     });
 #pragma unroll
     for (int r = 0; r < R; ++r) {
-        const float v = warp_sum(acc[r]);
-        if (lane == 0 && r < rows) {
-            const int64_t slot = tile_slots[r];
-            if (COMBINE) partial[slot * w.N + n] = v;
-            else st_act(y, slot * w.N + n, v);
+        if (r < rows) {  // warp-uniform: a tile of one or two slots pays for one or two reductions, not sixteen
+            const float v = warp_sum(acc[r]);
+            if (lane == 0) {
+                const int64_t slot = tile_slots[r];
+                if (COMBINE) partial[slot * w.N + n] = v;
+                else st_act(y, slot * w.N + n, v);
+            }
         }
     }
 }
@@ -315,7 +317,8 @@ int gather_grouped(const char *fn, const void *x, const StackView &w, int64_t E,
         SB_TRY(grouped_umma(fn, x, w, wsi, M, A, y, nullptr, act, /*combine=*/false, st));
         return 0;
     }
-    const int64_t Tmax = M * A / 16 + E + 2;
+    // tiles that can exist: S / 16 full ones + one ragged tile per non-empty bucket (at most S buckets, E + 1 with the invalid one)
+    const int64_t Tmax = M * A / 16 + (E + 1 < M * A ? E + 1 : M * A) + 1;
     SB_CHECK(Tmax <= 65535, fn, ": ", Tmax, " tile slots exceed the grid");
     const dim3 grid((unsigned)((w.N + 7) / 8), (unsigned)Tmax), block(256);
     if (act == kF32) grouped_f32_kernel<float, false><<<grid, block, 0, st>>>((const float *)x, w, wsi, A, (float *)y, nullptr);
@@ -340,7 +343,7 @@ int combine_grouped(const char *fn, const void *h, const StackView &w, int64_t E
     if (math != STRIX_MATH_F32) {
         SB_TRY(grouped_umma(fn, h, w, wsi, M, A, nullptr, partial, act, /*combine=*/true, st));
     } else {
-        const int64_t Tmax = M * A / 16 + E + 2;
+        const int64_t Tmax = M * A / 16 + (E + 1 < M * A ? E + 1 : M * A) + 1;  // as in gather_grouped
         SB_CHECK(Tmax <= 65535, fn, ": ", Tmax, " tile slots exceed the grid");
         const dim3 grid((unsigned)((w.N + 7) / 8), (unsigned)Tmax), block(256);
         if (act == kF32) grouped_f32_kernel<float, true><<<grid, block, 0, st>>>((const float *)h, w, wsi, A, nullptr, partial);
