@@ -154,6 +154,10 @@ __device__ __forceinline__ void load_x32(const uint16_t *x, int64_t off, float (
 // The 32 codes of chunk c (codes 32c .. 32c + 31) of one packed row, as floats. BITS 4: 16 bytes of nibbles (low
 // nibble = even k). 5: + one u32 of 5th bits (code i at bit i). 6: + two u32 of bits 4..5 (code i at bits 2(i%16) of
 // word i/16). 8: 32 bytes. Row starts are 16-byte aligned for every format the entry points accept.
+// A code (< 2^23) as a float without the quarter-rate integer conversion: 2^23 + code has the code in its low mantissa
+// bits, and subtracting 2^23 is exact.
+__device__ __forceinline__ float code_f(uint32_t code) { return __uint_as_float(0x4B000000u | code) - 8388608.0f; }
+
 template <int BITS>
 __device__ __forceinline__ void load_codes32(const uint8_t *row, int64_t K, int64_t c, float (&q)[32]) {
     if constexpr (BITS == 8) {
@@ -161,23 +165,23 @@ __device__ __forceinline__ void load_codes32(const uint8_t *row, int64_t K, int6
         const uint4 a = p[0], b = p[1];
         const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
 #pragma unroll
-        for (int i = 0; i < 32; ++i) q[i] = (float)((w[i / 4] >> (8 * (i % 4))) & 0xFFu);
+        for (int i = 0; i < 32; ++i) q[i] = code_f((w[i / 4] >> (8 * (i % 4))) & 0xFFu);
     } else {
         const uint4 a = *reinterpret_cast<const uint4 *>(row + c * 16);
         const uint32_t w[4] = {a.x, a.y, a.z, a.w};
         if constexpr (BITS == 4) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) q[i] = (float)((w[i / 8] >> (4 * (i % 8))) & 0xFu);
+            for (int i = 0; i < 32; ++i) q[i] = code_f((w[i / 8] >> (4 * (i % 8))) & 0xFu);
         } else if constexpr (BITS == 5) {
             const uint32_t hb = *reinterpret_cast<const uint32_t *>(row + K / 2 + c * 4);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) q[i] = (float)(((w[i / 8] >> (4 * (i % 8))) & 0xFu) | (((hb >> i) & 1u) << 4));
+            for (int i = 0; i < 32; ++i) q[i] = code_f(((w[i / 8] >> (4 * (i % 8))) & 0xFu) | (((hb >> i) & 1u) << 4));
         } else {
             const uint2 hb = *reinterpret_cast<const uint2 *>(row + K / 2 + c * 8);
             const uint32_t h[2] = {hb.x, hb.y};
 #pragma unroll
             for (int i = 0; i < 32; ++i)
-                q[i] = (float)(((w[i / 8] >> (4 * (i % 8))) & 0xFu) | (((h[i / 16] >> (2 * (i % 16))) & 3u) << 4));
+                q[i] = code_f(((w[i / 8] >> (4 * (i % 8))) & 0xFu) | (((h[i / 16] >> (2 * (i % 16))) & 3u) << 4));
         }
     }
 }
