@@ -206,6 +206,38 @@ __device__ __forceinline__ float row_partial(const uint8_t *row, const uint16_t 
     return acc;
 }
 
+// The same for two rows against the same activations: x is loaded once per chunk and used for both (these kernels are
+// bound by the L1 traffic of the activation loads, 128 bytes per 16 bytes of 4-bit codes). Each row's arithmetic is
+// exactly row_partial's.
+template <int BITS, typename T>
+__device__ __forceinline__ void row_partial2(const uint8_t *row0, const uint8_t *row1, const uint16_t *srow0, const uint16_t *mrow0,
+                                             const uint16_t *srow1, const uint16_t *mrow1, const T *x, int64_t K, int G, int64_t first,
+                                             int64_t stride, float &acc0, float &acc1) {
+    acc0 = 0.f, acc1 = 0.f;
+    for (int64_t c = first; c < K / 32; c += stride) {
+        float xv[32], q[32];
+        load_x32(x, c * 32, xv);
+        float xs = 0.f;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) xs += xv[i];
+        const int64_t g = c * 32 / G;
+        {
+            load_codes32<BITS>(row0, K, c, q);
+            float dot = 0.f;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) dot = fmaf(xv[i], q[i], dot);
+            acc0 = fmaf(bf16_bits_to_f32(srow0[g]), dot, fmaf(bf16_bits_to_f32(mrow0[g]), xs, acc0));
+        }
+        {
+            load_codes32<BITS>(row1, K, c, q);
+            float dot = 0.f;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) dot = fmaf(xv[i], q[i], dot);
+            acc1 = fmaf(bf16_bits_to_f32(srow1[g]), dot, fmaf(bf16_bits_to_f32(mrow1[g]), xs, acc1));
+        }
+    }
+}
+
 // Per-expert formats: a stack of E experts, N rows each. bits_tab / q_off null = one format (bits) for all, expert e's
 // rows at q + e * N * row_bytes; else expert e's format is bits_tab[e] and its rows start at q + q_off[e].
 struct StackView {

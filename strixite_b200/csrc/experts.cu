@@ -36,15 +36,18 @@ __global__ void __launch_bounds__(kWarps * 32)
         constexpr int BITS = decltype(bc)::value;
         const uint8_t *rows = w.rows(id, BITS);
         const int64_t r0 = (int64_t)id * w.N + j;
-        float g = row_partial<BITS>(rows + j * row_bytes(BITS, w.K), w.scale + r0 * gpr, w.minv + r0 * gpr, xr, w.K, (int)w.G, lane, 32);
-        g = warp_sum(g);
         if constexpr (SWIGLU) {
+            // gate row j and up row j share every activation load
             const int64_t ju = j + out_rows, r1 = r0 + out_rows;
-            float u = row_partial<BITS>(rows + ju * row_bytes(BITS, w.K), w.scale + r1 * gpr, w.minv + r1 * gpr, xr, w.K, (int)w.G, lane, 32);
-            u = warp_sum(u);
+            float g, u;
+            row_partial2<BITS>(rows + j * row_bytes(BITS, w.K), rows + ju * row_bytes(BITS, w.K), w.scale + r0 * gpr, w.minv + r0 * gpr,
+                               w.scale + r1 * gpr, w.minv + r1 * gpr, xr, w.K, (int)w.G, lane, 32, g, u);
+            g = warp_sum(g), u = warp_sum(u);
             // g and u as their store and reload would give them, h formed as the swiglu kernel forms it.
             if (lane == 0) st_act(y, slot * out_rows + j, as_stored(silu_f(as_stored(g, y)), y) * as_stored(u, y));
         } else {
+            float g = row_partial<BITS>(rows + j * row_bytes(BITS, w.K), w.scale + r0 * gpr, w.minv + r0 * gpr, xr, w.K, (int)w.G, lane, 32);
+            g = warp_sum(g);
             if (lane == 0) st_act(y, slot * out_rows + j, g);
         }
     });
@@ -55,8 +58,10 @@ __global__ void __launch_bounds__(kWarps * 32)
     experts_combine_kernel(const T *h, StackView w, int64_t E, const int32_t *ids, const float *coef, int64_t A, T *y,
                            uint32_t *err) {
     const int lane = threadIdx.x & 31;
-    const int64_t n = (int64_t)blockIdx.x * kWarps + (threadIdx.x >> 5);
+    // two output rows per warp: both read the same h chunks, which are the L1 traffic that bounds this kernel
+    const int64_t n = ((int64_t)blockIdx.x * kWarps + (threadIdx.x >> 5)) * 2;
     if (n >= w.N) return;
+    const int64_t n1 = n + 1 < w.N ? n + 1 : n;  // an odd last row is computed twice and stored once
     const int64_t m = blockIdx.y;
     int64_t first_bad = -1;
     for (int64_t a = 0; a < A; ++a) {
@@ -65,24 +70,32 @@ __global__ void __launch_bounds__(kWarps * 32)
     }
     if (first_bad >= 0) {
         if (n == 0 && lane == 0) raise_err(err, (uint32_t)ids[m * A + first_bad], (uint32_t)(m * A + first_bad));
-        if (lane == 0) st_act(y, m * w.N + n, qnan());
+        if (lane == 0) {
+            st_act(y, m * w.N + n, qnan());
+            if (n1 != n) st_act(y, m * w.N + n1, qnan());
+        }
         return;
     }
     const int64_t gpr = w.K / w.G;
-    float acc = 0.f;
+    float acc0 = 0.f, acc1 = 0.f;
     for (int64_t a = 0; a < A; ++a) {
         const int32_t id = ids[m * A + a];
         const int bits = w.bits_of(id);
-        const int64_t r = (int64_t)id * w.N + n;
+        const int64_t r0 = (int64_t)id * w.N + n, r1 = (int64_t)id * w.N + n1;
         by_bits(bits, [&](auto bc) {
             constexpr int BITS = decltype(bc)::value;
-            const float p = row_partial<BITS>(w.rows(id, BITS) + n * row_bytes(BITS, w.K), w.scale + r * gpr, w.minv + r * gpr,
-                                              h + (m * A + a) * w.K, w.K, (int)w.G, lane, 32);
-            acc = fmaf(coef[m * A + a], p, acc);
+            const uint8_t *rows = w.rows(id, BITS);
+            float p0, p1;
+            row_partial2<BITS>(rows + n * row_bytes(BITS, w.K), rows + n1 * row_bytes(BITS, w.K), w.scale + r0 * gpr, w.minv + r0 * gpr,
+                               w.scale + r1 * gpr, w.minv + r1 * gpr, h + (m * A + a) * w.K, w.K, (int)w.G, lane, 32, p0, p1);
+            acc0 = fmaf(coef[m * A + a], p0, acc0), acc1 = fmaf(coef[m * A + a], p1, acc1);
         });
     }
-    acc = warp_sum(acc);
-    if (lane == 0) st_act(y, m * w.N + n, acc);
+    acc0 = warp_sum(acc0), acc1 = warp_sum(acc1);
+    if (lane == 0) {
+        st_act(y, m * w.N + n, acc0);
+        if (n1 != n) st_act(y, m * w.N + n1, acc1);
+    }
 }
 
 enum Op { kGather, kGatherSwiglu, kCombine };
@@ -120,8 +133,8 @@ int experts(const char *fn, Op op, const void *x, const StackView &w, int64_t E,
     const dim3 block(kWarps * 32);
     auto go = [&](auto tag) {
         using T = decltype(tag);
-        if (op == kCombine)
-            experts_combine_kernel<T><<<dim3(bx, (unsigned)M), block, 0, st>>>((const T *)x, w, E, ids, coef, A, (T *)y, err);
+        if (op == kCombine)  // two output rows per warp
+            experts_combine_kernel<T><<<dim3((unsigned)((out_rows + 2 * kWarps - 1) / (2 * kWarps)), (unsigned)M), block, 0, st>>>((const T *)x, w, E, ids, coef, A, (T *)y, err);
         else if (op == kGatherSwiglu)
             experts_gather_kernel<T, true><<<dim3(bx, (unsigned)A, (unsigned)M), block, 0, st>>>((const T *)x, w, E, ids, A, (T *)y, err);
         else
