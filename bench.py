@@ -39,7 +39,7 @@ WORKLOADS = {
     "ep_prefill16384": dict(M=16384, d=2048, I=512, E=512, k=10, act="bf16", router="bf16", shared="stacked", mix=None, bias="zipf", ring=2, layers=1,
                             math=2, ep=True),
     # grouped_min: these shapes do not fit the fused decode kernel; of the per-function paths the per-slot kernels measure faster
-    # than the grouped ones at six tokens (3.4 ms against 4.9 ms per step), so the grouped path is switched off here
+    # than the grouped ones at six tokens (1.6 ms against 4.9 ms per step), so the grouped path is switched off here
     "stack4": dict(M=6, d=4096, I=1024, E=512, k=10, act="f32", router="f32", shared="stacked", mix=[0.6, 0.15, 0.15, 0.1], bias=None, ring=2,
                    layers=4, grouped_min=1000),
 }

@@ -206,34 +206,29 @@ __device__ __forceinline__ float row_partial(const uint8_t *row, const uint16_t 
     return acc;
 }
 
-// The same for two rows against the same activations: x is loaded once per chunk and used for both (these kernels are
+// The same for NR rows against the same activations: x is loaded once per chunk and used for every row (these kernels are
 // bound by the L1 traffic of the activation loads, 128 bytes per 16 bytes of 4-bit codes). Each row's arithmetic is
-// exactly row_partial's.
-template <int BITS, typename T>
-__device__ __forceinline__ void row_partial2(const uint8_t *row0, const uint8_t *row1, const uint16_t *srow0, const uint16_t *mrow0,
-                                             const uint16_t *srow1, const uint16_t *mrow1, const T *x, int64_t K, int G, int64_t first,
-                                             int64_t stride, float &acc0, float &acc1) {
-    acc0 = 0.f, acc1 = 0.f;
+// exactly row_partial's. row[r], srow[r], mrow[r]: the rows' code bytes, scales and minimums.
+template <int BITS, int NR, typename T>
+__device__ __forceinline__ void row_partial_n(const uint8_t *const (&row)[NR], const uint16_t *const (&srow)[NR], const uint16_t *const (&mrow)[NR],
+                                              const T *x, int64_t K, int G, int64_t first, int64_t stride, float (&acc)[NR]) {
+#pragma unroll
+    for (int r = 0; r < NR; ++r) acc[r] = 0.f;
     for (int64_t c = first; c < K / 32; c += stride) {
-        float xv[32], q[32];
+        float xv[32];
         load_x32(x, c * 32, xv);
         float xs = 0.f;
 #pragma unroll
         for (int i = 0; i < 32; ++i) xs += xv[i];
         const int64_t g = c * 32 / G;
-        {
-            load_codes32<BITS>(row0, K, c, q);
+#pragma unroll
+        for (int r = 0; r < NR; ++r) {
+            float q[32];
+            load_codes32<BITS>(row[r], K, c, q);
             float dot = 0.f;
 #pragma unroll
             for (int i = 0; i < 32; ++i) dot = fmaf(xv[i], q[i], dot);
-            acc0 = fmaf(bf16_bits_to_f32(srow0[g]), dot, fmaf(bf16_bits_to_f32(mrow0[g]), xs, acc0));
-        }
-        {
-            load_codes32<BITS>(row1, K, c, q);
-            float dot = 0.f;
-#pragma unroll
-            for (int i = 0; i < 32; ++i) dot = fmaf(xv[i], q[i], dot);
-            acc1 = fmaf(bf16_bits_to_f32(srow1[g]), dot, fmaf(bf16_bits_to_f32(mrow1[g]), xs, acc1));
+            acc[r] = fmaf(bf16_bits_to_f32(srow[r][g]), dot, fmaf(bf16_bits_to_f32(mrow[r][g]), xs, acc[r]));
         }
     }
 }

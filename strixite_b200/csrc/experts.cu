@@ -20,13 +20,18 @@ __global__ void __launch_bounds__(kWarps * 32)
     experts_gather_kernel(const T *x, StackView w, int64_t E, const int32_t *ids, int64_t A, T *y, uint32_t *err) {
     const int lane = threadIdx.x & 31;
     const int64_t out_rows = SWIGLU ? w.N / 2 : w.N;
-    const int64_t j = (int64_t)blockIdx.x * kWarps + (threadIdx.x >> 5);
+    // SWIGLU: two outputs per warp = four weight rows (gate j, j + 1, up j, j + 1) against one pass over the activations
+    const int64_t j = ((int64_t)blockIdx.x * kWarps + (threadIdx.x >> 5)) * (SWIGLU ? 2 : 1);
     if (j >= out_rows) return;
+    const int64_t j1 = SWIGLU && j + 1 < out_rows ? j + 1 : j;  // an odd last output is computed twice and stored once
     const int64_t m = blockIdx.z, slot = m * A + blockIdx.y;
     const int32_t id = ids[slot];
     if (id < 0 || id >= E) {
         if (j == 0 && lane == 0) raise_err(err, (uint32_t)id, (uint32_t)slot);
-        if (lane == 0) st_act(y, slot * out_rows + j, qnan());
+        if (lane == 0) {
+            st_act(y, slot * out_rows + j, qnan());
+            if (j1 != j) st_act(y, slot * out_rows + j1, qnan());
+        }
         return;
     }
     const int bits = w.bits_of(id);
@@ -35,18 +40,23 @@ __global__ void __launch_bounds__(kWarps * 32)
     by_bits(bits, [&](auto bc) {
         constexpr int BITS = decltype(bc)::value;
         const uint8_t *rows = w.rows(id, BITS);
-        const int64_t r0 = (int64_t)id * w.N + j;
+        const int64_t rb = row_bytes(BITS, w.K), r0 = (int64_t)id * w.N;
         if constexpr (SWIGLU) {
-            // gate row j and up row j share every activation load
-            const int64_t ju = j + out_rows, r1 = r0 + out_rows;
-            float g, u;
-            row_partial2<BITS>(rows + j * row_bytes(BITS, w.K), rows + ju * row_bytes(BITS, w.K), w.scale + r0 * gpr, w.minv + r0 * gpr,
-                               w.scale + r1 * gpr, w.minv + r1 * gpr, xr, w.K, (int)w.G, lane, 32, g, u);
-            g = warp_sum(g), u = warp_sum(u);
+            const int64_t rr[4] = {j, j1, j + out_rows, j1 + out_rows};
+            const uint8_t *const row[4] = {rows + rr[0] * rb, rows + rr[1] * rb, rows + rr[2] * rb, rows + rr[3] * rb};
+            const uint16_t *const sr[4] = {w.scale + (r0 + rr[0]) * gpr, w.scale + (r0 + rr[1]) * gpr, w.scale + (r0 + rr[2]) * gpr, w.scale + (r0 + rr[3]) * gpr};
+            const uint16_t *const mr[4] = {w.minv + (r0 + rr[0]) * gpr, w.minv + (r0 + rr[1]) * gpr, w.minv + (r0 + rr[2]) * gpr, w.minv + (r0 + rr[3]) * gpr};
+            float a[4];
+            row_partial_n<BITS, 4>(row, sr, mr, xr, w.K, (int)w.G, lane, 32, a);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) a[i] = warp_sum(a[i]);
             // g and u as their store and reload would give them, h formed as the swiglu kernel forms it.
-            if (lane == 0) st_act(y, slot * out_rows + j, as_stored(silu_f(as_stored(g, y)), y) * as_stored(u, y));
+            if (lane == 0) {
+                st_act(y, slot * out_rows + j, as_stored(silu_f(as_stored(a[0], y)), y) * as_stored(a[2], y));
+                if (j1 != j) st_act(y, slot * out_rows + j1, as_stored(silu_f(as_stored(a[1], y)), y) * as_stored(a[3], y));
+            }
         } else {
-            float g = row_partial<BITS>(rows + j * row_bytes(BITS, w.K), w.scale + r0 * gpr, w.minv + r0 * gpr, xr, w.K, (int)w.G, lane, 32);
+            float g = row_partial<BITS>(rows + j * rb, w.scale + (r0 + j) * gpr, w.minv + (r0 + j) * gpr, xr, w.K, (int)w.G, lane, 32);
             g = warp_sum(g);
             if (lane == 0) st_act(y, slot * out_rows + j, g);
         }
@@ -58,10 +68,13 @@ __global__ void __launch_bounds__(kWarps * 32)
     experts_combine_kernel(const T *h, StackView w, int64_t E, const int32_t *ids, const float *coef, int64_t A, T *y,
                            uint32_t *err) {
     const int lane = threadIdx.x & 31;
-    // two output rows per warp: both read the same h chunks, which are the L1 traffic that bounds this kernel
-    const int64_t n = ((int64_t)blockIdx.x * kWarps + (threadIdx.x >> 5)) * 2;
+    // four output rows per warp: all read the same h chunks, which are the L1 traffic that bounds this kernel
+    constexpr int NR = 4;
+    const int64_t n = ((int64_t)blockIdx.x * kWarps + (threadIdx.x >> 5)) * NR;
     if (n >= w.N) return;
-    const int64_t n1 = n + 1 < w.N ? n + 1 : n;  // an odd last row is computed twice and stored once
+    int64_t nn[NR];
+#pragma unroll
+    for (int r = 0; r < NR; ++r) nn[r] = n + r < w.N ? n + r : n;  // rows past the end repeat row n and are not stored
     const int64_t m = blockIdx.y;
     int64_t first_bad = -1;
     for (int64_t a = 0; a < A; ++a) {
@@ -70,32 +83,34 @@ __global__ void __launch_bounds__(kWarps * 32)
     }
     if (first_bad >= 0) {
         if (n == 0 && lane == 0) raise_err(err, (uint32_t)ids[m * A + first_bad], (uint32_t)(m * A + first_bad));
-        if (lane == 0) {
-            st_act(y, m * w.N + n, qnan());
-            if (n1 != n) st_act(y, m * w.N + n1, qnan());
-        }
+        if (lane == 0)
+            for (int r = 0; r < NR; ++r)
+                if (r == 0 || nn[r] != n) st_act(y, m * w.N + nn[r], qnan());
         return;
     }
     const int64_t gpr = w.K / w.G;
-    float acc0 = 0.f, acc1 = 0.f;
+    float acc[NR] = {0.f, 0.f, 0.f, 0.f};
     for (int64_t a = 0; a < A; ++a) {
         const int32_t id = ids[m * A + a];
         const int bits = w.bits_of(id);
-        const int64_t r0 = (int64_t)id * w.N + n, r1 = (int64_t)id * w.N + n1;
         by_bits(bits, [&](auto bc) {
             constexpr int BITS = decltype(bc)::value;
             const uint8_t *rows = w.rows(id, BITS);
-            float p0, p1;
-            row_partial2<BITS>(rows + n * row_bytes(BITS, w.K), rows + n1 * row_bytes(BITS, w.K), w.scale + r0 * gpr, w.minv + r0 * gpr,
-                               w.scale + r1 * gpr, w.minv + r1 * gpr, h + (m * A + a) * w.K, w.K, (int)w.G, lane, 32, p0, p1);
-            acc0 = fmaf(coef[m * A + a], p0, acc0), acc1 = fmaf(coef[m * A + a], p1, acc1);
+            const int64_t rb = row_bytes(BITS, w.K), r0 = (int64_t)id * w.N;
+            const uint8_t *const row[NR] = {rows + nn[0] * rb, rows + nn[1] * rb, rows + nn[2] * rb, rows + nn[3] * rb};
+            const uint16_t *const sr[NR] = {w.scale + (r0 + nn[0]) * gpr, w.scale + (r0 + nn[1]) * gpr, w.scale + (r0 + nn[2]) * gpr, w.scale + (r0 + nn[3]) * gpr};
+            const uint16_t *const mr[NR] = {w.minv + (r0 + nn[0]) * gpr, w.minv + (r0 + nn[1]) * gpr, w.minv + (r0 + nn[2]) * gpr, w.minv + (r0 + nn[3]) * gpr};
+            float p[NR];
+            row_partial_n<BITS, NR>(row, sr, mr, h + (m * A + a) * w.K, w.K, (int)w.G, lane, 32, p);
+#pragma unroll
+            for (int r = 0; r < NR; ++r) acc[r] = fmaf(coef[m * A + a], p[r], acc[r]);
         });
     }
-    acc0 = warp_sum(acc0), acc1 = warp_sum(acc1);
-    if (lane == 0) {
-        st_act(y, m * w.N + n, acc0);
-        if (n1 != n) st_act(y, m * w.N + n1, acc1);
-    }
+#pragma unroll
+    for (int r = 0; r < NR; ++r) acc[r] = warp_sum(acc[r]);
+    if (lane == 0)
+        for (int r = 0; r < NR; ++r)
+            if (r == 0 || nn[r] != n) st_act(y, m * w.N + nn[r], acc[r]);
 }
 
 enum Op { kGather, kGatherSwiglu, kCombine };
@@ -133,10 +148,10 @@ int experts(const char *fn, Op op, const void *x, const StackView &w, int64_t E,
     const dim3 block(kWarps * 32);
     auto go = [&](auto tag) {
         using T = decltype(tag);
-        if (op == kCombine)  // two output rows per warp
-            experts_combine_kernel<T><<<dim3((unsigned)((out_rows + 2 * kWarps - 1) / (2 * kWarps)), (unsigned)M), block, 0, st>>>((const T *)x, w, E, ids, coef, A, (T *)y, err);
-        else if (op == kGatherSwiglu)
-            experts_gather_kernel<T, true><<<dim3(bx, (unsigned)A, (unsigned)M), block, 0, st>>>((const T *)x, w, E, ids, A, (T *)y, err);
+        if (op == kCombine)  // four output rows per warp
+            experts_combine_kernel<T><<<dim3((unsigned)((out_rows + 4 * kWarps - 1) / (4 * kWarps)), (unsigned)M), block, 0, st>>>((const T *)x, w, E, ids, coef, A, (T *)y, err);
+        else if (op == kGatherSwiglu)  // two outputs per warp
+            experts_gather_kernel<T, true><<<dim3((unsigned)((out_rows + 2 * kWarps - 1) / (2 * kWarps)), (unsigned)A, (unsigned)M), block, 0, st>>>((const T *)x, w, E, ids, A, (T *)y, err);
         else
             experts_gather_kernel<T, false><<<dim3(bx, (unsigned)A, (unsigned)M), block, 0, st>>>((const T *)x, w, E, ids, A, (T *)y, err);
     };
