@@ -11,14 +11,18 @@ namespace {
 
 using namespace sb;
 
-constexpr int kWarps = 8;  // output rows per block
+constexpr int kWarps = 8;  // output rows per block at most
+
+// Few output rows (a router projection: ~500 rows of a long K) would fill fewer blocks of 8 rows than the GPU has SMs: two
+// rows per block then.
+inline int rows_per_block(int64_t N) { return N >= 8 * 2 * sm_count() ? kWarps : 2; }
 
 template <int BITS, typename TX, typename TY, int MR>
 __global__ void __launch_bounds__(kWarps * 32)
     linear_q_kernel(const TX *x, const uint8_t *q, const uint16_t *scale, const uint16_t *minv, TY *y, int64_t M,
                     int64_t N, int64_t K, int G) {
     const int lane = threadIdx.x & 31;
-    const int64_t n = (int64_t)blockIdx.x * kWarps + (threadIdx.x >> 5);
+    const int64_t n = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (n >= N) return;
     const int64_t m0 = (int64_t)blockIdx.y * MR;
     const int rows = (int)(M - m0 < MR ? M - m0 : MR);
@@ -55,7 +59,7 @@ template <typename TW, typename TX, typename TY, int MR>
 __global__ void __launch_bounds__(kWarps * 32)
     linear_w_kernel(const TX *x, const TW *w, TY *y, int64_t M, int64_t N, int64_t K) {
     const int lane = threadIdx.x & 31;
-    const int64_t n = (int64_t)blockIdx.x * kWarps + (threadIdx.x >> 5);
+    const int64_t n = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (n >= N) return;
     const int64_t m0 = (int64_t)blockIdx.y * MR;
     const int rows = (int)(M - m0 < MR ? M - m0 : MR);
@@ -94,7 +98,8 @@ int pick_mr(int64_t M) { return M == 1 ? 1 : M == 2 ? 2 : M <= 4 ? 4 : 8; }
 template <int BITS, typename TX, typename TY>
 void launch_q(const TX *x, const strix_qview &w, TY *y, int64_t M, cudaStream_t st) {
     const int mr = pick_mr(M);
-    const dim3 grid((unsigned)((w.N + kWarps - 1) / kWarps), (unsigned)((M + mr - 1) / mr)), block(kWarps * 32);
+    const int rpb = rows_per_block(w.N);
+    const dim3 grid((unsigned)((w.N + rpb - 1) / rpb), (unsigned)((M + mr - 1) / mr)), block(rpb * 32);
     switch (mr) {
         case 1: linear_q_kernel<BITS, TX, TY, 1><<<grid, block, 0, st>>>(x, w.q, w.scale, w.minv, y, M, w.N, w.K, (int)w.G); break;
         case 2: linear_q_kernel<BITS, TX, TY, 2><<<grid, block, 0, st>>>(x, w.q, w.scale, w.minv, y, M, w.N, w.K, (int)w.G); break;
@@ -134,7 +139,8 @@ int linear_q(const char *fn, const void *x, const strix_qview *wp, void *y, int6
 template <typename TW, typename TX, typename TY>
 void launch_w(const TX *x, const TW *w, TY *y, int64_t M, int64_t N, int64_t K, cudaStream_t st) {
     const int mr = pick_mr(M);
-    const dim3 grid((unsigned)((N + kWarps - 1) / kWarps), (unsigned)((M + mr - 1) / mr)), block(kWarps * 32);
+    const int rpb = rows_per_block(N);
+    const dim3 grid((unsigned)((N + rpb - 1) / rpb), (unsigned)((M + mr - 1) / mr)), block(rpb * 32);
     switch (mr) {
         case 1: linear_w_kernel<TW, TX, TY, 1><<<grid, block, 0, st>>>(x, w, y, M, N, K); break;
         case 2: linear_w_kernel<TW, TX, TY, 2><<<grid, block, 0, st>>>(x, w, y, M, N, K); break;
