@@ -246,8 +246,10 @@ typedef struct strix_moe_layer_desc {
     int math;                   /* STRIX_MATH_* of the grouped path */
     int64_t tensor_min_tokens;  /* math != STRIX_MATH_F32: forwards of at least this many tokens run the tensor-core path
                                  * (0 = the default, 64); below it the FP32 kernels run */
-    int decode_impl;            /* forwards of <= 8 tokens: 0 = the fused single-kernel path where the shapes allow it,
-                                 * 1 = the per-function kernels in the reference's sequence */
+    int decode_impl;            /* forwards of <= 8 tokens: 0 = the single streaming kernel where the shapes allow it (d and I
+                                 * multiples of 128, 4/5/6-bit projections in groups of 128, 8-bit ones in groups of 64 or
+                                 * 128; activations are F16 operands there, |x| and |h| up to 65504), 1 = the
+                                 * per-function kernels in the reference's sequence */
 } strix_moe_layer_desc;
 
 typedef struct strix_moe_layer strix_moe_layer;
@@ -280,7 +282,9 @@ int strix_moe_combine_reduce(const float *partial, const int64_t *pos, const int
                              int64_t A, int64_t E, int64_t N, void *y, int act, void *stream);
 /* Device pointer of a named intermediate of the last forward - the reference's probes (runtime/qwen4exp.hpp:179-188):
  * "router_logits" f32 [M, E(+1)], "router_ids" i32 [M, A], "router_coef" f32 [M, A], "experts_h" [M, A, I],
- * "shared_h" [M, I], "shared_y" [M, d], "err" u32 [6] (router words 0..2, expert words 3..5), "group_ws". */
+ * "shared_h" [M, I], "shared_y" [M, d], "err" u32 [6] (router words 0..2, expert words 3..5), "group_ws", and
+ * "decode_sync": the streaming decode kernel's barrier words, NULL when forwards of <= 8 tokens run the per-function
+ * kernels instead (shapes or group sizes it does not take). */
 const void *strix_moe_layer_probe(strix_moe_layer *layer, const char *name);
 /* Zeroes the layer's error words. */
 int strix_moe_layer_reset_errors(strix_moe_layer *layer, void *stream);

@@ -23,7 +23,7 @@ NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--extended-lambda",
     "-Xcompiler", "-fPIC", "-I", os.path.join(ROOT, "include"), "-I", CSRC,
-]
+] + os.environ.get("STRIX_NVCC_FLAGS", "").split()  # e.g. -DSTRIX_PROFILE for a diagnostic build (phase timestamps, wait counters)
 
 
 def _newest_header():

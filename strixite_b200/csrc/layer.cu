@@ -3,7 +3,7 @@
 // Nothing here computes: it validates, owns workspaces, picks the per-slot or grouped experts path and enqueues.
 #include "common.cuh"
 
-#include "decode_fused.cuh"
+#include "decode_stream.cuh"
 #include "prefill_umma.cuh"
 #include "strixite_b200.h"
 
@@ -67,11 +67,11 @@ struct strix_moe_layer {
     uint32_t *pin_err = nullptr;
     void *dev_x = nullptr, *dev_y = nullptr;
     int64_t last_M = 0;
-    // the fused decode kernel's scratch and plan
+    // the streaming decode kernel's scratch and plan
     uint8_t *hrec = nullptr;
     uint32_t *sync = nullptr;
     bool fused_ok = false;
-    sb::DecodeParams plan{};
+    sb::StreamParams plan{};
     // the tensor-core path for many tokens (math != F32, uniform 4-bit stacks)
     sb::PrefillPlan *prefill = nullptr;
     int64_t tensor_min = 64;
@@ -165,34 +165,45 @@ int strix_moe_layer_create(const strix_moe_layer_desc *desc, strix_moe_layer **o
     a(dev_alloc((char **)&L->dev_x, (size_t)(T * d.d * es), "x staging"));
     a(dev_alloc((char **)&L->dev_y, (size_t)(T * d.d * es), "y staging"));
     {
-        // Fused decode kernel: its shared-memory plan for up to 8 tokens, the h records and the barrier words.
-        sb::DecodeParams &p = L->plan;
+        // Streaming decode kernel: its shared-memory plan for up to 8 tokens, the h records and the barrier words.
+        sb::StreamParams &p = L->plan;
         const int64_t Mf = T < 8 ? T : 8;
         p.M = (int)Mf, p.d = (int)d.d, p.I = (int)d.I, p.E = (int)d.E, p.k = (int)d.k, p.A = (int)L->A, p.R = (int)L->router_rows,
         p.Estack = (int)L->Estack, p.act = d.act, p.shared_mode = d.shared_mode, p.gated = L->gated ? 1 : 0;
-        int bits_gu = d.experts_mixed ? 8 : d.gate_up_bits, bits_dn = d.experts_mixed ? 8 : d.down_bits;
-        int64_t minG = d.experts_mixed ? (d.gate_up_mix.G < d.down_mix.G ? d.gate_up_mix.G : d.down_mix.G) : (d.gate_up.G < d.down.G ? d.gate_up.G : d.down.G);
+        // the smallest group size among the 4/5/6-bit projections and among the 8-bit ones the kernel will stream
+        int64_t g_nib = 128, g_q8 = 128;
         bool aligned = true;
         auto al = [&](const void *q) { aligned = aligned && sb::aligned16(q); };
-        if (d.experts_mixed) al(d.gate_up_mix.scale), al(d.gate_up_mix.minv), al(d.down_mix.scale), al(d.down_mix.minv);
-        else al(d.gate_up.scale), al(d.gate_up.minv), al(d.down.scale), al(d.down.minv);
-        if (d.shared_mode == STRIX_SHARED_SEPARATE) {
-            bits_gu = d.sh_gate_up_bits > bits_gu ? d.sh_gate_up_bits : bits_gu, bits_dn = d.sh_down_bits > bits_dn ? d.sh_down_bits : bits_dn;
-            minG = d.sh_gate_up.G < minG ? d.sh_gate_up.G : minG, minG = d.sh_down.G < minG ? d.sh_down.G : minG;
-            al(d.sh_gate_up.scale), al(d.sh_gate_up.minv), al(d.sh_down.scale), al(d.sh_down.minv), al(d.sh_gate_up.q), al(d.sh_down.q);
+        auto seen = [&](int bits, int64_t G) {
+            int64_t &g = bits == 8 ? g_q8 : g_nib;
+            g = G < g ? G : g;
+        };
+        if (d.experts_mixed) {
+            al(d.gate_up_mix.scale), al(d.gate_up_mix.minv), al(d.down_mix.scale), al(d.down_mix.minv), al(d.gate_up_mix.q), al(d.down_mix.q);
+            seen(4, d.gate_up_mix.G), seen(8, d.gate_up_mix.G), seen(4, d.down_mix.G), seen(8, d.down_mix.G);
+        } else {
+            al(d.gate_up.scale), al(d.gate_up.minv), al(d.down.scale), al(d.down.minv), al(d.gate_up.q), al(d.down.q);
+            seen(d.gate_up_bits, d.gate_up.G), seen(d.down_bits, d.down.G);
         }
-        // the expert formats the kernel will meet (bit 0: 4 bits, 1: 5, 2: 6, 3: 8): picks the kernel variant
-        auto fbit = [](int bits) { return bits == 4 ? 1 : bits == 5 ? 2 : bits == 6 ? 4 : 8; };
-        p.fmask = d.experts_mixed ? 0xF : (fbit(d.gate_up_bits) | fbit(d.down_bits));
-        if (d.shared_mode == STRIX_SHARED_SEPARATE) p.fmask |= fbit(d.sh_gate_up_bits) | fbit(d.sh_down_bits);
-        p.g128_4bit = !d.experts_mixed && (d.gate_up_bits != 4 || d.gate_up.G == 128) && (d.down_bits != 4 || d.down.G == 128);
-        if (d.shared_mode == STRIX_SHARED_SEPARATE)
-            p.g128_4bit = p.g128_4bit && (d.sh_gate_up_bits != 4 || d.sh_gate_up.G == 128) && (d.sh_down_bits != 4 || d.sh_down.G == 128);
-        L->fused_ok = rc == 0 && aligned && d.decode_impl == 0 && sb::decode_fused_plan(p, bits_gu, bits_dn, (int)minG) != 0;
+        if (d.shared_mode == STRIX_SHARED_SEPARATE) {
+            al(d.sh_gate_up.scale), al(d.sh_gate_up.minv), al(d.sh_down.scale), al(d.sh_down.minv), al(d.sh_gate_up.q), al(d.sh_down.q);
+            seen(d.sh_gate_up_bits, d.sh_gate_up.G), seen(d.sh_down_bits, d.sh_down.G);
+        }
+        if (d.router_kind != STRIX_ROUTER_Q) al(d.router_w);
+        else al(d.router_q.q), aligned = aligned && d.router_bits == 8;  // quantized routers: 8-bit rows only
+        {
+            const bool experts_q4 = !d.experts_mixed && d.gate_up_bits == 4 && d.down_bits == 4;
+            const bool sep = d.shared_mode == STRIX_SHARED_SEPARATE;
+            if (experts_q4 && (!sep || (d.sh_gate_up_bits == 4 && d.sh_down_bits == 4))) p.format_set = 0;
+            else if (experts_q4 && sep && d.sh_gate_up_bits == 8 && d.sh_down_bits == 8 && d.sh_gate_up.G == 64 && d.sh_down.G == 64) p.format_set = 1;
+            else p.format_set = 2;
+        }
+        L->fused_ok = rc == 0 && aligned && d.decode_impl == 0 && sb::decode_stream_plan(p, (int)Mf, (int)g_nib, (int)g_q8) != 0;
         if (L->fused_ok) {
-            a(dev_alloc(&L->hrec, (size_t)((Mf * L->A + Mf) * p.hrec_bytes), "fused decode h records"));
-            a(dev_alloc(&L->sync, 128, "fused decode barrier words"));
-            if (rc == 0 && cudaMemset(L->sync, 0, 512) != cudaSuccess) rc = STRIX_ERR_CUDA;
+            const size_t hbytes = (size_t)p.n_rec_max * (size_t)p.rec_bytes;
+            a(dev_alloc(&L->hrec, hbytes, "decode h records"));
+            a(dev_alloc(&L->sync, 128, "decode barrier words"));
+            if (rc == 0 && (cudaMemset(L->sync, 0, 512) != cudaSuccess || cudaMemset(L->hrec, 0, hbytes) != cudaSuccess)) rc = STRIX_ERR_CUDA;
         }
     }
     L->tensor_min = d.tensor_min_tokens > 0 ? d.tensor_min_tokens : kPrefillMinTokens;
@@ -243,8 +254,9 @@ int strix_moe_layer_forward(strix_moe_layer *L, const void *x, int64_t M, void *
 
     if (L->fused_ok && M <= 8 && !(L->prefill != nullptr && M >= L->tensor_min)) {
         // Decode / verify: the whole sublayer in one persistent kernel.
-        sb::DecodeParams p = L->plan;
-        p.M = (int)M, p.x = x, p.y = y;
+        sb::StreamParams p = L->plan;
+        sb::decode_stream_set_tokens(p, (int)M);
+        p.x = x, p.y = y;
         p.router_kind = d.router_kind, p.router_bits = d.router_bits, p.router_w = d.router_w, p.router_q = d.router_q, p.router_bias = d.router_bias;
         if (d.experts_mixed) {
             p.gate_up = sb::StackView{d.gate_up_mix.q, d.gate_up_mix.scale, d.gate_up_mix.minv, d.gate_up_mix.bits, d.gate_up_mix.q_off, 0, d.gate_up_mix.N, d.gate_up_mix.K, d.gate_up_mix.G};
@@ -256,7 +268,7 @@ int strix_moe_layer_forward(strix_moe_layer *L, const void *x, int64_t M, void *
         p.sh_gate_up_bits = d.sh_gate_up_bits, p.sh_down_bits = d.sh_down_bits, p.sh_gate_up = d.sh_gate_up, p.sh_down = d.sh_down;
         p.logits = L->logits, p.ids = L->ids, p.coef = L->coef, p.hh = L->hh, p.sh_h = L->sh_h, p.hrec = L->hrec, p.err = L->err, p.sync = L->sync;
         // the plan was made for min(max_tokens, 8) tokens; fewer tokens only leave more room
-        SB_TRY(sb::decode_fused_launch(fn, p, st));
+        SB_TRY(sb::decode_stream_launch(fn, p, st));
         return 0;
     }
     // 1. Router logits, FP32 [M, R]; row E (when gated) is the shared expert's gate.
@@ -384,7 +396,7 @@ const void *strix_moe_layer_probe(strix_moe_layer *L, const char *name) {
     if (!std::strcmp(name, "shared_y")) return L->sh_y;
     if (!std::strcmp(name, "err")) return L->err;
     if (!std::strcmp(name, "group_ws")) return L->group_ws;
-    if (!std::strcmp(name, "fused_sync")) return L->sync;
+    if (!std::strcmp(name, "decode_sync")) return L->sync;  // null when forwards of <= 8 tokens run the per-function kernels
     return nullptr;
 }
 

@@ -229,6 +229,11 @@ int strix_check_router_error(const uint32_t *err, const char *what) {
 }
 
 int strix_report_expert_error(const uint32_t e[3], const char *what) {
+    // {2, 0xdec000 | code, block}: a bounded wait of the single-kernel decode path ran out (0x105 / 0x200: a grid barrier, here /
+    // elsewhere in the grid; 0x107: the copy of the hidden records); the layer's outputs of that forward are not valid
+    SB_CHECK(!(e[0] == 2 && (e[1] & 0xfff000u) == 0xdec000u), what ? what : "", ": the decode kernel gave up a bounded wait (code 0x",
+             std::hex, (e[1] & 0xfffu), std::dec, ", block ", e[2], "); outputs of that forward are not valid - reset the layer's error words "
+             "(strix_moe_layer_reset_errors) before the next forward");
     SB_CHECK(e[0] == 0, what ? what : "", ": expert id ", (int32_t)e[1], " at slot ", e[2],
              " (token * A + a) is out of range; outputs for that token are NaN");
     return 0;

@@ -118,6 +118,12 @@ class MoeLayer:
              K._s(stream))
         return partial
 
+    @property
+    def streams_decode(self):
+        """True when forwards of at most 8 tokens run the single streaming decode kernel (its shapes and formats fit);
+        False when they run the per-function kernels in the reference's sequence."""
+        return bool(lib.strix_moe_layer_probe(self._h, b"decode_sync"))
+
     def reset_errors(self, stream=None):
         call("strix_moe_layer_reset_errors", self._h, K._s(stream))
 
@@ -129,7 +135,7 @@ class MoeLayer:
         shapes = {
             "router_logits": ((M, self.router_rows), torch.float32), "router_ids": ((M, self.A), torch.int32),
             "router_coef": ((M, self.A), torch.float32), "experts_h": ((M, self.A, self.I), K._dtype(self.act)),
-            "shared_h": ((M, self.I), K._dtype(self.act)), "shared_y": ((M, self.d), K._dtype(self.act)), "err": ((6,), torch.int32), "fused_sync": ((128,), torch.int32),
+            "shared_h": ((M, self.I), K._dtype(self.act)), "shared_y": ((M, self.d), K._dtype(self.act)), "err": ((6,), torch.int32), "decode_sync": ((128,), torch.int32),
         }
         bf16 = shapes[name][1] == torch.bfloat16
         shape, dt = shapes[name]

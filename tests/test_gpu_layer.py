@@ -81,6 +81,56 @@ def test_fused_decode_formats_and_token_counts(M, cfg):
         run_and_check(L, x, act, max_tokens=8)
 
 
+@pytest.mark.parametrize("M", (1, 2, 4, 5, 6, 8))
+@pytest.mark.parametrize("cfg", [dict(expert_bits=5, G=128, router="bf16", shared="stacked"),
+                                 dict(mix=[0.25, 0.25, 0.25, 0.25], G=128, router="q8", shared="separate", shared_bits=6, shared_G=128),
+                                 dict(mix=[0.4, 0.2, 0.2, 0.2], G=128, router="f32", shared="separate", shared_bits=8, shared_G=64),
+                                 dict(expert_bits=4, G=128, router="q8", shared=None)])
+def test_streaming_decode_formats_and_token_counts(M, cfg):
+    # every format of the streaming kernel (groups of 128; the 8-bit shared expert also in groups of 64), one and two F16
+    # planes (FP32 activations of at most 4 tokens carry the rounding remainder), an intermediate size of one chunk
+    L = make_layer(140 + M, d=512, I=128 if M == 5 else 256, E=20, k=4, **cfg)
+    for act in (oracle.F32, oracle.BF16):
+        x = randn_act(np.random.default_rng(150 + M), (M, 512), act)
+        layer, e = run_and_check(L, x, act, max_tokens=8)
+        assert layer.streams_decode
+        if act == oracle.F32 and M <= 4:
+            assert e < 2e-5  # two planes: FP32-like
+
+
+def test_streaming_decode_probes_match_the_oracle():
+    # the intermediate h of the routed experts (the probe) against the oracle's, slot by slot
+    L = make_layer(171, d=512, I=256, E=20, k=4, G=128, router="f32", shared="stacked", mix=[0.25, 0.25, 0.25, 0.25])
+    x = randn_act(np.random.default_rng(172), (6, 512), oracle.F32)
+    layer, _ = run_and_check(L, x, oracle.F32, max_tokens=8)
+    _, it = oracle.moe_layer(x, L)
+    h = layer.probe("experts_h", 6).cpu().numpy()
+    assert rel_err_rows(h.reshape(-1, 256), np.asarray(it["h"], np.float32).reshape(-1, 256)) < 2e-3
+
+
+@pytest.mark.parametrize("kind", ("all_equal", "pairs", "one_hot_block"))
+def test_streaming_decode_router_ties(kind):
+    # tied logits inside the single-kernel path: ties go to the lower index (strixite kernels/moe_router.hpp:11-23), also when
+    # far more logits tie at the top-k boundary than the candidate list of the kernel holds
+    E, k, d = 96, 6, 512
+    L = make_layer(180, d=d, I=128, E=E, k=k, G=128, router="f32", shared="stacked")
+    r = L["router"]
+    if kind == "all_equal":
+        r[:E] = 0.0                      # every routed logit is 0: experts 0..k-1
+    elif kind == "pairs":
+        r[1:E:2] = r[0:E:2]              # rows 2i and 2i+1 equal: both or the lower one
+    else:
+        r[:E] = 0.0
+        r[40:80] = r[E][None, :] * 0 + 0.01  # forty logits tie above the rest
+    for M in (1, 5):
+        x = randn_act(np.random.default_rng(181 + M), (M, d), oracle.F32)
+        layer, _ = run_and_check(L, x, oracle.F32, max_tokens=8)
+        assert layer.streams_decode
+        ids = layer.probe("router_ids", M).cpu().numpy()
+        if kind == "all_equal":
+            assert np.array_equal(ids[:, :k], np.tile(np.arange(k, dtype=np.int32), (M, 1)))
+
+
 def test_fused_decode_repeated_experts_across_tokens():
     # identical tokens route identically: every expert group carries all tokens (the dedup path at its fullest)
     L = make_layer(60, d=512, I=128, E=16, k=4, G=128, router="f32", shared="stacked")
