@@ -270,8 +270,8 @@ int strix_moe_stack_forward(strix_moe_layer *const *layers, int64_t n_layers, vo
  * routed to several local experts is sent once. partial[i, :] = W_down[ids[i]] * SwiGLU(W_gate_up[ids[i]] * row) in FP32,
  * without the routing coefficient. Groups the slots by expert and runs the tensor-core kernels; needs a layer created
  * with math != STRIX_MATH_F32 over uniform 4-bit stacks, and n <= max_tokens * (k + shared). Slots with an invalid id
- * raise the expert error words and are left unwritten. No counterpart in the reference (which has no expert
- * parallelism). */
+ * raise the expert error words and are left unwritten; an id of -2 marks an absent slot (padding of a fixed-capacity list):
+ * skipped without an error. No counterpart in the reference (which has no expert parallelism). */
 int strix_moe_layer_experts_partial(strix_moe_layer *layer, const void *rows, const int32_t *row_index, const int32_t *ids,
                                     int64_t n, float *partial, void *stream);
 /* The ordered weighted sum of the reference's combine (kernels/moe_grouped.hpp:60-62, second half): y[m, :] = sum over a
@@ -280,6 +280,34 @@ int strix_moe_layer_experts_partial(strix_moe_layer *layer, const void *rows, co
  * came back from other devices in another order are summed where they lie. */
 int strix_moe_combine_reduce(const float *partial, const int64_t *pos, const int32_t *ids, const float *coef, int64_t M,
                              int64_t A, int64_t E, int64_t N, void *y, int act, void *stream);
+/* ---- expert parallelism: the device side of the token exchange. No counterpart in the reference (one device). -------------
+ * A rank sends every token once to each rank that owns one of its experts, in FIXED-capacity blocks per (source, destination)
+ * pair so that no size goes through the host: C rows [C, d] and strix_ep_meta_ints(C, Cs) int32 of metadata -
+ * {n_rows, n_slots, 0, 0}, per row {first slot, slots}, per slot {local expert id, row, coefficient bits} - all in token
+ * order. P <= 8 ranks. */
+int64_t strix_ep_meta_ints(int64_t C, int64_t Cs);
+/* Home rank, after moe_router: ids / coef [T, A] (id E = the stacked shared expert, kept home; an invalid id stays home with
+ * local id -1 and poisons the token), owner / local_of [E + 1] (rank and local index of every routed expert) ->
+ * rowtok [P, C] (the token behind every row to send), meta [P, MW], pos [T, P] (row of token t in destination r's block, or
+ * -1). flags[0] / flags[1] receive the largest row / slot count that exceeded C / Cs (0 = the step fitted). */
+int strix_ep_plan(const int32_t *ids, const float *coef, int64_t T, int64_t A, int64_t E, const int32_t *owner,
+                  const int32_t *local_of, int P, int rank, int64_t C, int64_t Cs, int32_t *rowtok, int32_t *meta, int32_t *pos,
+                  uint32_t *flags, void *stream);
+/* rows_send[r, i, :] = x[rowtok[r, i], :] for the rows the plan counted. */
+int strix_ep_gather_rows(const void *x, int64_t d, int act, const int32_t *rowtok, const int32_t *meta, int P, int64_t C,
+                         int64_t Cs, void *rows_send, void *stream);
+/* Expert rank: the received metadata [P, MW] as one slot list of P * Cs entries for strix_moe_layer_experts_partial -
+ * slot_ids (-2 = absent, beyond a pair's count) and slot_row (the slot's row among the P * C received rows). */
+int strix_ep_unpack(const int32_t *meta_recv, int P, int64_t C, int64_t Cs, int32_t *slot_ids, int32_t *slot_row,
+                    void *stream);
+/* Expert rank: summed[s, i, :] = sum over row (s, i)'s slots, in slot order, of coef * partial[slot, :] (FP32). */
+int strix_ep_row_sum(const float *partial, const int32_t *meta_recv, int P, int64_t C, int64_t Cs, int64_t d,
+                     float *summed, void *stream);
+/* Home rank: y[t, :] = the returned rows back[r, pos[t, r], :] added in ascending r, rounded once to `act`; NaN for a token
+ * with an id outside [0, E]. */
+int strix_ep_home_sum(const float *back, const int32_t *pos, const int32_t *ids, int64_t T, int64_t A, int64_t E, int P,
+                      int64_t C, int64_t d, void *y, int act, void *stream);
+
 /* Device pointer of a named intermediate of the last forward - the reference's probes (runtime/qwen4exp.hpp:179-188):
  * "router_logits" f32 [M, E(+1)], "router_ids" i32 [M, A], "router_coef" f32 [M, A], "experts_h" [M, A, I],
  * "shared_h" [M, I], "shared_y" [M, d], "err" u32 [6] (router words 0..2, expert words 3..5), "group_ws", and

@@ -1,0 +1,263 @@
+// Expert parallelism: the device side of the token exchange. The routed experts of a layer are spread over P ranks; a rank
+// routes its own tokens, sends every token ONCE to each rank that owns one of its experts, the expert rank runs the experts
+// and adds coef * partial over the token's slots it served, and the home rank adds the returned rows in rank order.
+// strixite runs one device (runtime/qwen4exp.cpp:1126-1186), so none of this has a counterpart there.
+//
+// The exchange uses FIXED capacities so that no size ever goes through the host: per (source, destination) pair C rows and Cs
+// slots. A pair's message is one block of rows [C, d] and one block of MW = 4 + 2 C + 3 Cs int32 of metadata:
+//   [0..3]              n_rows, n_slots, 0, 0
+//   [4 + 2 i ..]        row i: first slot, number of slots          (slots of a row are consecutive, in slot order)
+//   [4 + 2 C + 3 j ..]  slot j: local expert id on the destination, row (inside the pair's block), coefficient bits
+// Everything is in token order per destination, so the layout is a pure function of the routing.
+#include "common.cuh"
+
+#include "strixite_b200.h"
+
+namespace {
+
+using namespace sb;
+
+constexpr int kMaxRanks = 8;
+constexpr int kPlanThreads = 1024;
+
+// Exclusive scan of one int per thread over the block; *total receives the sum. warp_tot: 32 ints of shared memory.
+__device__ int plan_scan(int v, int *warp_tot, int *total) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int incl = v;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+        const int o = __shfl_up_sync(0xffffffffu, incl, off);
+        if (lane >= off) incl += o;
+    }
+    if (lane == 31) warp_tot[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+        int t = warp_tot[lane], ti = t;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+            const int o = __shfl_up_sync(0xffffffffu, ti, off);
+            if (lane >= off) ti += o;
+        }
+        warp_tot[lane] = ti - t;
+        if (lane == 31) *total = ti;
+    }
+    __syncthreads();
+    const int res = warp_tot[warp] + incl - v;
+    __syncthreads();
+    return res;
+}
+
+// The destination of slot id: its owner; the stacked shared expert (id == E) and invalid ids stay on the home rank (an
+// invalid id keeps local id -1 there, which poisons the token like on one device).
+__device__ __forceinline__ void slot_dest(int32_t id, int E, const int32_t *owner, const int32_t *local_of, int rank, int &r, int &loc) {
+    if (id >= 0 && id <= E) r = id == E ? rank : owner[id], loc = local_of[id];
+    else r = rank, loc = -1;
+}
+
+// One block. Thread i owns the contiguous tokens [i * tpt, (i + 1) * tpt): pass 1 counts its rows and slots per destination,
+// block scans turn the counts into first positions, pass 2 writes. Everything lands in token order.
+__global__ void __launch_bounds__(kPlanThreads)
+    ep_plan_kernel(const int32_t *ids, const float *coef, int T, int A, int E, const int32_t *owner, const int32_t *local_of, int P, int rank, int C,
+                   int Cs, int32_t *rowtok, int32_t *meta, int32_t *pos, uint32_t *flags) {
+    __shared__ int warp_tot[32];
+    __shared__ int tot_rows[kMaxRanks], tot_slots[kMaxRanks];
+    const int t0 = threadIdx.x, MW = 4 + 2 * C + 3 * Cs;
+    const int tpt = (T + kPlanThreads - 1) / kPlanThreads;
+    const int tb = min(T, t0 * tpt), te = min(T, tb + tpt);
+    int rows[kMaxRanks], slots[kMaxRanks];
+#pragma unroll
+    for (int r = 0; r < kMaxRanks; ++r) rows[r] = 0, slots[r] = 0;
+    for (int t = tb; t < te; ++t) {
+        unsigned seen = 0;
+        for (int a = 0; a < A; ++a) {
+            int r, loc;
+            slot_dest(ids[t * A + a], E, owner, local_of, rank, r, loc);
+#pragma unroll
+            for (int q = 0; q < kMaxRanks; ++q)
+                if (q == r) slots[q] += 1, rows[q] += !(seen >> q & 1u);
+            seen |= 1u << r;
+        }
+    }
+    int row0[kMaxRanks], slot0[kMaxRanks];
+#pragma unroll
+    for (int r = 0; r < kMaxRanks; ++r) {
+        row0[r] = 0, slot0[r] = 0;
+        if (r < P) {
+            row0[r] = plan_scan(rows[r], warp_tot, &tot_rows[r]);
+            slot0[r] = plan_scan(slots[r], warp_tot, &tot_slots[r]);
+        }
+    }
+    if (t0 < P) {
+        const int nr = tot_rows[t0], ns = tot_slots[t0];
+        if (nr > C) atomicMax(&flags[0], (uint32_t)nr);
+        if (ns > Cs) atomicMax(&flags[1], (uint32_t)ns);
+        int32_t *m = meta + (int64_t)t0 * MW;
+        m[0] = min(nr, C), m[1] = min(ns, Cs), m[2] = 0, m[3] = 0;
+    }
+    for (int t = tb; t < te; ++t) {
+        // a token's slots per destination, in slot order; the row is opened by its first slot there
+        int row_of[kMaxRanks];
+#pragma unroll
+        for (int r = 0; r < kMaxRanks; ++r) row_of[r] = -1;
+        for (int a = 0; a < A; ++a) {
+            int r, loc;
+            slot_dest(ids[t * A + a], E, owner, local_of, rank, r, loc);
+#pragma unroll
+            for (int q = 0; q < kMaxRanks; ++q) {
+                if (q != r) continue;
+                int32_t *m = meta + (int64_t)q * MW;
+                if (row_of[q] < 0) {
+                    row_of[q] = row0[q]++;
+                    if (row_of[q] < C) {
+                        rowtok[(int64_t)q * C + row_of[q]] = t;
+                        m[4 + 2 * row_of[q]] = slot0[q], m[4 + 2 * row_of[q] + 1] = 0;
+                    }
+                }
+                const int j = slot0[q]++;
+                if (j < Cs && row_of[q] < C) {
+                    int32_t *sm = m + 4 + 2 * C + 3 * j;
+                    sm[0] = loc, sm[1] = row_of[q], sm[2] = __float_as_int(coef[t * A + a]);
+                    m[4 + 2 * row_of[q] + 1] += 1;  // this thread owns the row
+                }
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < kMaxRanks; ++r)
+            if (r < P) pos[(int64_t)t * P + r] = row_of[r] < C ? row_of[r] : -1;
+    }
+}
+
+// Row i of the block for destination r <- x[rowtok[r][i]]; one block per row, 16 bytes per thread and step.
+__global__ void __launch_bounds__(256) ep_gather_rows_kernel(const uint4 *x, int row16, const int32_t *rowtok, const int32_t *meta, int C, int MW, uint4 *rows_send) {
+    const int r = blockIdx.y, i = blockIdx.x;
+    if (i >= meta[(int64_t)r * MW]) return;
+    const uint4 *src = x + (int64_t)rowtok[(int64_t)r * C + i] * row16;
+    uint4 *dst = rows_send + ((int64_t)r * C + i) * row16;
+    for (int j = threadIdx.x; j < row16; j += 256) dst[j] = src[j];
+}
+
+// The received slot lists as one list of P * Cs entries for the experts: local expert id (-2 = absent: beyond the pair's count)
+// and the slot's activation row among all received rows.
+__global__ void __launch_bounds__(256) ep_unpack_kernel(const int32_t *meta, int P, int C, int Cs, int32_t *slot_ids, int32_t *slot_row) {
+    const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    if (i >= (int64_t)P * Cs) return;
+    const int s = (int)(i / Cs), j = (int)(i - (int64_t)s * Cs);
+    const int32_t *m = meta + (int64_t)s * (4 + 2 * C + 3 * Cs);
+    if (j < m[1]) {
+        const int32_t *sm = m + 4 + 2 * C + 3 * j;
+        slot_ids[i] = sm[0], slot_row[i] = s * C + sm[1];
+    } else {
+        slot_ids[i] = -2, slot_row[i] = 0;
+    }
+}
+
+// Expert side: summed[s][i][:] = sum over the row's slots, in slot order, of coef * partial[slot][:] (FP32, fmaf as the
+// reference's combine, strixite kernels/moe_grouped.hip:456-472). One block per received row.
+__global__ void __launch_bounds__(256) ep_row_sum_kernel(const float4 *partial, const int32_t *meta, int C, int Cs, int d4, float4 *summed) {
+    const int s = blockIdx.y, i = blockIdx.x;
+    const int32_t *m = meta + (int64_t)s * (4 + 2 * C + 3 * Cs);
+    if (i >= m[0]) return;
+    const int first = m[4 + 2 * i], n = m[4 + 2 * i + 1];
+    const int32_t *sm = m + 4 + 2 * C + 3 * first;
+    for (int j = threadIdx.x; j < d4; j += 256) {
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int q = 0; q < n; ++q) {
+            const float c = __int_as_float(sm[3 * q + 2]);
+            const float4 p = partial[((int64_t)s * Cs + first + q) * d4 + j];
+            v.x = fmaf(c, p.x, v.x), v.y = fmaf(c, p.y, v.y), v.z = fmaf(c, p.z, v.z), v.w = fmaf(c, p.w, v.w);
+        }
+        summed[((int64_t)s * C + i) * d4 + j] = v;
+    }
+}
+
+// Home side: y[t][:] = the rows that came back for token t, added in ascending rank order, rounded once to the activation
+// dtype. A token the router failed (ids -1) or with an invalid id gets a NaN row, as on one device.
+template <typename T>
+__global__ void __launch_bounds__(256) ep_home_sum_kernel(const float4 *back, const int32_t *pos, const int32_t *ids, int A, int E, int P, int C, int d4, T *y) {
+    const int t = blockIdx.x;
+    bool bad = false;
+    for (int a = 0; a < A; ++a) {
+        const int32_t id = ids[(int64_t)t * A + a];
+        bad |= id < 0 || id > E;
+    }
+    for (int j = threadIdx.x; j < d4; j += 256) {
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int r = 0; r < P; ++r) {
+            const int p = pos[(int64_t)t * P + r];
+            if (p < 0) continue;
+            const float4 b = back[((int64_t)r * C + p) * d4 + j];
+            v.x += b.x, v.y += b.y, v.z += b.z, v.w += b.w;
+        }
+        if (bad) v = make_float4(qnan(), qnan(), qnan(), qnan());
+        const int64_t o = ((int64_t)t * d4 + j) * 4;
+        st_act(y, o, v.x), st_act(y, o + 1, v.y), st_act(y, o + 2, v.z), st_act(y, o + 3, v.w);
+    }
+}
+
+}  // namespace
+
+extern "C" {
+
+int64_t strix_ep_meta_ints(int64_t C, int64_t Cs) { return 4 + 2 * C + 3 * Cs; }
+
+int strix_ep_plan(const int32_t *ids, const float *coef, int64_t T, int64_t A, int64_t E, const int32_t *owner, const int32_t *local_of, int P, int rank,
+                  int64_t C, int64_t Cs, int32_t *rowtok, int32_t *meta, int32_t *pos, uint32_t *flags, void *stream) {
+    const char *fn = "ep_plan";
+    SB_CHECK(ids && coef && owner && local_of && rowtok && meta && pos && flags, fn, ": null pointer");
+    SB_CHECK(P >= 1 && P <= kMaxRanks && rank >= 0 && rank < P, fn, ": ", P, " ranks (1..", kMaxRanks, "), rank ", rank);
+    SB_CHECK(T >= 1 && A >= 1 && A <= 64 && E >= 1 && T * A <= (1 << 22) && C >= 1 && Cs >= 1 && C <= (1 << 22) && Cs <= (1 << 24), fn, ": T = ", T, ", A = ", A,
+             ", E = ", E, ", C = ", C, ", Cs = ", Cs);
+    ep_plan_kernel<<<1, kPlanThreads, 0, static_cast<cudaStream_t>(stream)>>>(ids, coef, (int)T, (int)A, (int)E, owner, local_of, P, rank, (int)C, (int)Cs, rowtok, meta,
+                                                                              pos, flags);
+    SB_LAUNCH_OK(fn);
+    return 0;
+}
+
+int strix_ep_gather_rows(const void *x, int64_t d, int act, const int32_t *rowtok, const int32_t *meta, int P, int64_t C, int64_t Cs, void *rows_send, void *stream) {
+    const char *fn = "ep_gather_rows";
+    SB_CHECK(x && rowtok && meta && rows_send, fn, ": null pointer");
+    SB_CHECK(act_ok(act) && d >= 8 && (d * act_size(act)) % 16 == 0 && aligned16(x) && aligned16(rows_send), fn, ": rows of ", d, " ", act_name(act),
+             " values must be whole 16-byte pieces, 16-byte aligned");
+    SB_CHECK(P >= 1 && P <= kMaxRanks && C >= 1 && C <= 0x7fffffff, fn, ": P = ", P, ", C = ", C);
+    ep_gather_rows_kernel<<<dim3((unsigned)C, (unsigned)P), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint4 *>(x), (int)(d * act_size(act) / 16), rowtok, meta, (int)C, (int)strix_ep_meta_ints(C, Cs), static_cast<uint4 *>(rows_send));
+    SB_LAUNCH_OK(fn);
+    return 0;
+}
+
+int strix_ep_unpack(const int32_t *meta_recv, int P, int64_t C, int64_t Cs, int32_t *slot_ids, int32_t *slot_row, void *stream) {
+    const char *fn = "ep_unpack";
+    SB_CHECK(meta_recv && slot_ids && slot_row, fn, ": null pointer");
+    SB_CHECK(P >= 1 && P <= kMaxRanks && C >= 1 && Cs >= 1 && (int64_t)P * Cs <= (1 << 26), fn, ": P = ", P, ", C = ", C, ", Cs = ", Cs);
+    const int64_t n = (int64_t)P * Cs;
+    ep_unpack_kernel<<<(unsigned)((n + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(meta_recv, P, (int)C, (int)Cs, slot_ids, slot_row);
+    SB_LAUNCH_OK(fn);
+    return 0;
+}
+
+int strix_ep_row_sum(const float *partial, const int32_t *meta_recv, int P, int64_t C, int64_t Cs, int64_t d, float *summed, void *stream) {
+    const char *fn = "ep_row_sum";
+    SB_CHECK(partial && meta_recv && summed, fn, ": null pointer");
+    SB_CHECK(P >= 1 && P <= kMaxRanks && C >= 1 && Cs >= 1 && d >= 4 && d % 4 == 0 && aligned16(partial) && aligned16(summed), fn, ": P = ", P, ", C = ", C, ", d = ", d);
+    ep_row_sum_kernel<<<dim3((unsigned)C, (unsigned)P), 256, 0, static_cast<cudaStream_t>(stream)>>>(reinterpret_cast<const float4 *>(partial), meta_recv, (int)C, (int)Cs,
+                                                                                                  (int)(d / 4), reinterpret_cast<float4 *>(summed));
+    SB_LAUNCH_OK(fn);
+    return 0;
+}
+
+int strix_ep_home_sum(const float *back, const int32_t *pos, const int32_t *ids, int64_t T, int64_t A, int64_t E, int P, int64_t C, int64_t d, void *y, int act,
+                      void *stream) {
+    const char *fn = "ep_home_sum";
+    SB_CHECK(back && pos && ids && y, fn, ": null pointer");
+    SB_CHECK(P >= 1 && P <= kMaxRanks && T >= 1 && T <= 0x7fffffff && d >= 4 && d % 4 == 0 && act_ok(act) && aligned16(back), fn, ": P = ", P, ", T = ", T, ", d = ", d);
+    auto st = static_cast<cudaStream_t>(stream);
+    if (act == kF32)
+        ep_home_sum_kernel<float><<<(unsigned)T, 256, 0, st>>>(reinterpret_cast<const float4 *>(back), pos, ids, (int)A, (int)E, P, (int)C, (int)(d / 4), static_cast<float *>(y));
+    else
+        ep_home_sum_kernel<uint16_t><<<(unsigned)T, 256, 0, st>>>(reinterpret_cast<const float4 *>(back), pos, ids, (int)A, (int)E, P, (int)C, (int)(d / 4),
+                                                                  static_cast<uint16_t *>(y));
+    SB_LAUNCH_OK(fn);
+    return 0;
+}
+
+}  // extern "C"

@@ -134,6 +134,109 @@ __global__ void __launch_bounds__(kRouteThreads)
     }
 }
 
+// ---- the same grouping over many blocks (the layer object's path; it owns the scratch) -------------------------------
+// The slots are cut into kSegs contiguous segments, a warp each. Pass 1 counts every segment's slots per bucket into
+// scratch[seg][bucket]; pass 2 (one block) turns each bucket's column into the segments' first ranks, scans the bucket
+// totals and writes the header, the offsets and the tile tables; pass 3 places every segment's slots in slot order. The
+// result is the single-block kernel's, bit for bit. quiet: an id of -2 marks an absent slot (padding of a fixed-capacity
+// slot list): it lands in the invalid bucket like any bad id but raises no error.
+constexpr int kSegBlocks = 16, kSegWarps = 8, kSegs = kSegBlocks * kSegWarps;
+constexpr int kNoBad = 0x7f7f7f7f;  // "no invalid id seen": what a byte-wise memset can write
+
+__device__ __forceinline__ int seg_len(int S) { return ((S + kSegs - 1) / kSegs + 31) & ~31; }
+
+__global__ void __launch_bounds__(kSegWarps * 32) route_count_kernel(const int32_t *ids, int S, int E, int32_t *scratch, int quiet) {
+    extern __shared__ int smem[];
+    const int B = E + 1, t = threadIdx.x, lane = t & 31, warp = t >> 5, g = blockIdx.x * kSegWarps + warp;
+    int *cnt = smem + warp * B;
+    for (int i = lane; i < B; i += 32) cnt[i] = 0;
+    __syncwarp();
+    const int seg = seg_len(S), s_begin = min(S, g * seg), s_end = min(S, s_begin + seg);
+    int first_bad = 0x7fffffff;
+    for (int s = s_begin + lane; s < s_end; s += 32) {
+        const int32_t id = ids[s];
+        const bool bad = id < 0 || id >= E;
+        atomicAdd(&cnt[bad ? E : id], 1);
+        if (bad && !(quiet && id == -2) && s < first_bad) first_bad = s;
+    }
+    __syncwarp();
+    for (int i = lane; i < B; i += 32) scratch[g * B + i] = cnt[i];
+    first_bad = __reduce_min_sync(0xffffffffu, first_bad);
+    if (lane == 0 && first_bad != 0x7fffffff) atomicMin(&scratch[kSegs * B], first_bad);
+}
+
+__global__ void __launch_bounds__(kRouteThreads)
+    route_scan_kernel(const int32_t *ids, int S, int E, int Tmax, int WTmax, int32_t *ws, int32_t *scratch, uint32_t *err) {
+    extern __shared__ int smem[];
+    const int B = E + 1;
+    int *start = smem;               // [B + 1]
+    int *tile0 = start + B + 1;      // [B + 1]
+    int *wtile0 = tile0 + B + 1;     // [B + 1]
+    int *warp_tot = wtile0 + B + 1;  // [32]
+    __shared__ int total_a, total_b, total_c;
+    const int t = threadIdx.x;
+    if (t == 0) {
+        const int first_bad = scratch[kSegs * B];
+        if (first_bad != kNoBad) raise_err(err, (uint32_t)ids[first_bad], (uint32_t)first_bad);
+        scratch[kSegs * B] = kNoBad;  // ready for the next grouping
+    }
+    int count = 0;
+    if (t < B) {
+#pragma unroll 8
+        for (int g = 0; g < kSegs; ++g) {
+            const int c = scratch[g * B + t];
+            scratch[g * B + t] = count;  // this segment's first rank inside the bucket
+            count += c;
+        }
+    }
+    const int st = block_exclusive_scan(count, warp_tot, &total_a);
+    const int tl = block_exclusive_scan((count + 15) / 16, warp_tot, &total_b);
+    const int wt = block_exclusive_scan((count + 63) / 64, warp_tot, &total_c);
+    int32_t *offsets = ws + 4, *slots = offsets + E + 2, *tile_bucket = slots + S, *tile_start = tile_bucket + Tmax;
+    int32_t *wtile_bucket = tile_start + Tmax, *wtile_start = wtile_bucket + WTmax;
+    if (t < B) start[t] = st, tile0[t] = tl, wtile0[t] = wt, offsets[t] = st;
+    if (t == 0) {
+        start[B] = total_a, tile0[B] = total_b, wtile0[B] = total_c;
+        ws[0] = total_b, ws[1] = S, ws[2] = E, ws[3] = total_c;
+        offsets[E + 1] = total_a;
+    }
+    __syncthreads();
+    for (int i = t; i < total_b; i += kRouteThreads) {
+        const int b = bucket_of_tile(tile0, B, i);
+        tile_bucket[i] = b, tile_start[i] = start[b] + (i - tile0[b]) * 16;
+    }
+    for (int i = t; i < total_c; i += kRouteThreads) {
+        const int b = bucket_of_tile(wtile0, B, i);
+        wtile_bucket[i] = b, wtile_start[i] = start[b] + (i - wtile0[b]) * 64;
+    }
+}
+
+__global__ void __launch_bounds__(kSegWarps * 32) route_place_kernel(const int32_t *ids, int S, int E, int32_t *ws, const int32_t *scratch) {
+    extern __shared__ int smem[];
+    const int B = E + 1, t = threadIdx.x, lane = t & 31, warp = t >> 5, g = blockIdx.x * kSegWarps + warp;
+    int *pos = smem + warp * B;  // next position of each bucket for this segment
+    const int32_t *offsets = ws + 4;
+    int32_t *slots = ws + 4 + E + 2;
+    for (int i = lane; i < B; i += 32) pos[i] = offsets[i] + scratch[g * B + i];
+    __syncwarp();
+    const int seg = seg_len(S), s_begin = min(S, g * seg), s_end = min(S, s_begin + seg);
+    for (int s0 = s_begin; s0 < s_end; s0 += 32) {
+        const int s = s0 + lane;
+        const bool live = s < s_end;
+        int b = 0x40000000 | lane;  // idle lanes: a bucket of their own
+        if (live) {
+            const int32_t id = ids[s];
+            b = (id < 0 || id >= E) ? E : id;
+        }
+        const unsigned same = __match_any_sync(0xffffffffu, b);
+        const int rank = __popc(same & ((1u << lane) - 1u));
+        if (live) slots[pos[b] + rank] = s;
+        __syncwarp();
+        if (live && rank == 0) pos[b] += __popc(same);
+        __syncwarp();
+    }
+}
+
 // FP32 path: one tile (up to 16 slots of one expert) x 8 output rows per block, a warp per row. The row's codes are
 // decoded once per 32-code chunk and applied to every slot of the tile. COMBINE: inputs h[slot], outputs the per-slot
 // dots into `partial` (FP32); else inputs x[slot / A], outputs y[slot] in the activation dtype.
@@ -392,6 +495,29 @@ int mixed_view(const char *fn, const strix_qmix_view *w, StackView *out) {
 }
 
 }  // namespace
+
+namespace sb {
+
+size_t route_scratch_bytes(int64_t E) { return (size_t)(kSegs * (E + 1) + 1) * 4; }
+
+int route_scratch_init(void *scratch, int64_t E, cudaStream_t stream) {
+    // the counts are rewritten by every grouping; only the first-bad word has to start at "none"
+    SB_CUDA(cudaMemsetAsync(static_cast<int32_t *>(scratch) + kSegs * (E + 1), 0x7f, 4, stream), "route scratch");
+    return 0;
+}
+
+int group_routes_multi(const char *fn, const int32_t *ids, int64_t S, int64_t E, int32_t *ws, int32_t *scratch, uint32_t *err, bool quiet,
+                       cudaStream_t stream) {
+    const size_t seg_smem = (size_t)kSegWarps * (E + 1) * sizeof(int);
+    const size_t scan_smem = (size_t)(3 * (E + 2) + 32) * sizeof(int);
+    route_count_kernel<<<kSegBlocks, kSegWarps * 32, seg_smem, stream>>>(ids, (int)S, (int)E, scratch, quiet ? 1 : 0);
+    route_scan_kernel<<<1, kRouteThreads, scan_smem, stream>>>(ids, (int)S, (int)E, (int)(S / 16 + E + 2), (int)(S / 64 + E + 2), ws, scratch, err);
+    route_place_kernel<<<kSegBlocks, kSegWarps * 32, seg_smem, stream>>>(ids, (int)S, (int)E, ws, scratch);
+    SB_LAUNCH_OK(fn, ": grouping S=", S, " E=", E);
+    return 0;
+}
+
+}  // namespace sb
 
 extern "C" {
 

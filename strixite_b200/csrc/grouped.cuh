@@ -22,6 +22,14 @@ __host__ __device__ inline RouteTables route_tables(const int32_t *ws, int64_t S
     return t;
 }
 
+// The grouping of moe_group_routes over many blocks, for callers that own a scratch buffer of route_scratch_bytes(E) bytes
+// (initialized once with route_scratch_init; one buffer per stream that groups): same workspace contents as the public
+// single-block entry, bit for bit. quiet: ids of -2 are absent slots - invalid bucket, no error.
+size_t route_scratch_bytes(int64_t E);
+int route_scratch_init(void *scratch, int64_t E, cudaStream_t stream);
+int group_routes_multi(const char *fn, const int32_t *ids, int64_t S, int64_t E, int32_t *ws, int32_t *scratch, uint32_t *err, bool quiet,
+                       cudaStream_t stream);
+
 // Tensor-core grouped projection over a grouping workspace (grouped_umma.cu). combine = false: inputs x[slot / A],
 // outputs y[slot, :] in the activation dtype. combine = true: inputs h[slot], outputs FP32 partial[slot, :].
 int grouped_umma(const char *fn, const void *x, const StackView &w, const int32_t *ws, int64_t M, int64_t A, void *y,

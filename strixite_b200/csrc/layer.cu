@@ -4,6 +4,7 @@
 #include "common.cuh"
 
 #include "decode_stream.cuh"
+#include "grouped.cuh"
 #include "prefill_umma.cuh"
 #include "strixite_b200.h"
 
@@ -61,6 +62,7 @@ struct strix_moe_layer {
     float *partial = nullptr;
     void *group_ws = nullptr;
     size_t group_ws_bytes = 0;
+    int32_t *route_scratch = nullptr;  // per-segment counts of the multi-block grouping
     uint32_t *err = nullptr;       // [8]: router words 0..2, expert words 3..5
     // host staging
     void *pin_x = nullptr, *pin_y = nullptr;
@@ -161,6 +163,8 @@ int strix_moe_layer_create(const strix_moe_layer_desc *desc, strix_moe_layer **o
     L->group_ws_bytes = strix_moe_route_workspace_bytes(T, L->A, L->Estack);
     a(L->group_ws_bytes == 0 ? STRIX_ERR_CHECK : 0);
     a(dev_alloc((char **)&L->group_ws, L->group_ws_bytes, "grouping workspace"));
+    a(dev_alloc((char **)&L->route_scratch, sb::route_scratch_bytes(L->Estack), "grouping scratch"));
+    if (rc == 0) rc = sb::route_scratch_init(L->route_scratch, L->Estack, nullptr);
     a(dev_alloc(&L->err, 8, "error words"));
     a(dev_alloc((char **)&L->dev_x, (size_t)(T * d.d * es), "x staging"));
     a(dev_alloc((char **)&L->dev_y, (size_t)(T * d.d * es), "y staging"));
@@ -224,7 +228,7 @@ int strix_moe_layer_create(const strix_moe_layer_desc *desc, strix_moe_layer **o
 
 void strix_moe_layer_destroy(strix_moe_layer *L) {
     if (L == nullptr) return;
-    void *dev[] = {L->logits, L->ids, L->coef, L->ids_k, L->coef_k, L->gu, L->hh, L->sh_h, L->sh_y, L->partial, L->group_ws, L->err, L->dev_x, L->dev_y, L->hrec, L->sync};
+    void *dev[] = {L->logits, L->ids, L->coef, L->ids_k, L->coef_k, L->gu, L->hh, L->sh_h, L->sh_y, L->partial, L->group_ws, L->err, L->dev_x, L->dev_y, L->hrec, L->sync, L->route_scratch};
     for (void *p : dev)
         if (p) cudaFree(p);
     sb::prefill_destroy(L->prefill);
@@ -299,7 +303,7 @@ int strix_moe_layer_forward(strix_moe_layer *L, const void *x, int64_t M, void *
     if (tensor_path) {
         // many tokens on the tensor cores: bucket-ordered F16 activations, gate/up with SwiGLU in its epilogue, down into
         // FP32 partials, then the ordered reduction of the reference's combine
-        SB_TRY(strix_moe_group_routes(L->ids, M, A, L->Estack, L->group_ws, L->group_ws_bytes, expert_err, stream));
+        SB_TRY(sb::group_routes_multi(fn, L->ids, M * A, L->Estack, static_cast<int32_t *>(L->group_ws), L->route_scratch, expert_err, false, st));
         SB_TRY(sb::prefill_experts(L->prefill, x, nullptr, act, static_cast<const int32_t *>(L->group_ws), M, A, L->partial, st));
         SB_TRY(sb::combine_reduce(fn, L->partial, L->ids, L->coef, M, A, L->Estack, d.d, y, act, st));
     } else if (M >= d.grouped_min_tokens) {
@@ -343,7 +347,8 @@ int strix_moe_layer_experts_partial(strix_moe_layer *L, const void *rows, const 
     SB_CHECK(L->prefill != nullptr, fn, ": the layer has no tensor-core plan (needs math != F32, uniform 4-bit stacks, d % 256 == 0, I % 128 == 0 and max_tokens >= tensor_min_tokens)");
     SB_CHECK(n >= 1 && n <= L->d.max_tokens * L->A, fn, ": ", n, " rows, expected 1..", L->d.max_tokens * L->A);
     auto st = static_cast<cudaStream_t>(stream);
-    SB_TRY(strix_moe_group_routes(ids, n, 1, L->Estack, L->group_ws, L->group_ws_bytes, L->err + 3, stream));
+    // ids of -2 are absent slots (the padding of a fixed-capacity slot list): no error, never computed
+    SB_TRY(sb::group_routes_multi(fn, ids, n, L->Estack, static_cast<int32_t *>(L->group_ws), L->route_scratch, L->err + 3, true, st));
     SB_TRY(sb::prefill_experts(L->prefill, rows, row_index, L->d.act, static_cast<const int32_t *>(L->group_ws), n, 1, partial, st));
     return 0;
 }

@@ -1,247 +1,354 @@
-"""Expert-parallel MoE sublayer: the routed experts sharded over the ranks of a torch.distributed group, tokens
-data-parallel, one all-to-all each way.
+"""Expert-parallel MoE sublayer: the routed experts spread over the ranks of a torch.distributed group, tokens
+data-parallel, one all-to-all each way, no size ever passing through the host.
 
-strixite itself runs one device (its expert stacks are whole, runtime/qwen4exp.cpp:1126-1186), so this has no
-counterpart there; its contract is "the same output as the single-device layer":
+strixite itself runs one device (its expert stacks are whole, runtime/qwen4exp.cpp:1126-1186), so this has no counterpart
+there; its contract is "the same output as the single-device layer" to FP32 rounding (bit for bit on one rank).
 
-  home rank   router projection + moe_router on its own tokens (router weights replicated)       -> ids, coef [T, A]
-              every slot (token, a) goes to the rank that owns its expert; the stacked shared expert (id E) is
-              replicated and stays home (it is local expert E / P of every rank's stacks)
-  exchange    counts, then one activation row + one local expert id per slot (all_to_all_single, uneven splits)
-  expert rank partial[i, :] = W_down[e_i] * SwiGLU(W_gate_up[e_i] * row_i), FP32, no coefficient
-  exchange    the FP32 rows back, in the order they were sent
-  home rank   y[t, :] = sum_a coef[t, a] * partial[t * A + a, :] in ascending a: the reference's ordered combine
+  home rank    router projection + moe_router on its own tokens (router weights replicated)          -> ids, coef [T, A]
+               plan: a token goes ONCE to every rank that owns one of its experts, with its slots' local expert ids and
+               coefficients; the stacked shared expert (id E) is replicated and stays home
+  exchange     fixed-capacity blocks per (source, destination): C rows [C, d] and MW int32 of metadata (layout: csrc/ep.cu);
+               torch.distributed all_to_all_single with equal splits (NCCL on GPUs) - nothing is sized on the host
+  expert rank  partial[slot, :] = W_down[e] * SwiGLU(W_gate_up[e] * row) in FP32 over the received slots (absent slots of a
+               pair's capacity are skipped), then one FP32 row per received (token, rank): sum of coef * partial in slot order
+  exchange     those rows back
+  home rank    y[t, :] = the rows that came back for token t, added in ascending rank order, rounded once
 
-A slot's partial row depends on nothing but its own row and expert, and the final sum runs in slot order on the home
-rank, so the result does not depend on the number of ranks.
+Placement: which rank owns which expert is a table (contiguous blocks, or balanced over a load estimate so that a skewed router
+does not make one rank the straggler). A step may be cut into token chunks on separate streams so that one chunk's exchanges
+overlap the other's kernels.
 
-That is the exact mode (dedup=False). The default mode (dedup=True) moves less: a token's row goes ONCE to every rank that
-owns one of its experts (with its slots' expert ids and coefficients), the expert rank sums coef * partial over the
-token's slots it served (ascending slot order) and returns ONE FP32 row per (token, rank), and the home rank adds those
-in ascending rank order. Same arithmetic, another association: results are reproducible for a given number of ranks and
-agree with the single-device layer to FP32 rounding, not bit for bit.
-
-The exchange plumbing is torch (index_select / argsort / all_to_all_single on whatever device the tensors live on);
-the three compute steps are callables, by default the CUDA library's. Tests drive the same plumbing over gloo on CPU
-tensors with the oracle's functions plugged in.
+The compute steps come from a backend object: CudaBackend (this library's kernels) here; the tests drive the same exchange
+logic over gloo with a host backend made of numpy and the oracle.
 """
+import ctypes as C
+
+import numpy as np
 import torch
 import torch.distributed as dist
 
 
-class ExpertParallelMoe:
-    def __init__(self, E, k, world, rank, route_fn, experts_fn, reduce_fn, group=None, shared=True, dedup=True):
-        """E routed experts (E % world == 0), top-k; `shared`: a stacked shared expert with id E rides slot k.
-        route_fn(x) -> (ids int32 [T, A], coef float32 [T, A]);  experts_fn(rows [n, d], local_ids int32 [n]) -> float32 [n, d];
-        reduce_fn(partial float32 [R, d], pos int64 [T, W], ids int32 [T, W], coef float32 [T, W], out_dtype) -> [T, d]:
-        y[t] = sum over w ascending of coef[t, w] * partial[pos[t, w]] (ids only say valid / invalid), rounded once to
-        out_dtype (None = the activation dtype). With dedup, experts_fn(rows, local_ids, row_index int32 [n]) reads slot
-        i's activation from rows[row_index[i]]."""
-        if E % world != 0:
-            raise ValueError("ExpertParallelMoe: %d experts do not divide over %d ranks" % (E, world))
-        self.E, self.k, self.world, self.rank, self.group = E, k, world, rank, group
-        self.El = E // world
-        self.A = k + (1 if shared else 0)
-        self.route_fn, self.experts_fn, self.reduce_fn = route_fn, experts_fn, reduce_fn
-        self.dedup = dedup
-        self.last = {}
-
-    def plan(self, ids):
-        """Slots sorted by destination rank (stable, so a destination sees a home rank's slots in slot order).
-        Returns (order int64 [S], local expert ids int32 [S] in that order, counts int64 [world])."""
-        flat = ids.reshape(-1).to(torch.int64)
-        shared = flat == self.E
-        bad = (flat < 0) | (flat > self.E)
-        dest = torch.where(shared | bad, torch.full_like(flat, self.rank), torch.div(flat, self.El, rounding_mode="floor"))
-        local = torch.where(shared, torch.full_like(flat, self.El), flat - dest * self.El)
-        local = torch.where(bad, torch.full_like(flat, -1), local)  # invalid ids stay invalid: the kernels poison those tokens
-        order = torch.argsort(dest, stable=True)
-        counts = torch.bincount(dest, minlength=self.world)
-        return order, local[order].to(torch.int32), counts
-
-    def forward(self, x, timings=None):
-        """y [T, d] for this rank's tokens x [T, d]. timings: an optional dict that receives the milliseconds of each phase
-        (CUDA events; adds a synchronization at the end)."""
-        marks = []
-
-        def mark(name):
-            if timings is not None and x.is_cuda:
-                ev = torch.cuda.Event(enable_timing=True)
-                ev.record()
-                marks.append((name, ev))
-
-        mark("start")
-        y = self._forward_dedup(x, mark) if self.dedup else self._forward_exact(x, mark)
-        if marks:
-            torch.cuda.synchronize()
-            for (_, a), (name, b) in zip(marks[:-1], marks[1:]):
-                timings[name] = timings.get(name, 0.0) + a.elapsed_time(b)
-        return y
-
-    def _exchange_counts(self, counts):
-        """counts int64 [world, c] per destination -> what every source sends here, as host lists (split sizes are host ints)."""
-        recv = torch.empty_like(counts)
-        dist.all_to_all_single(recv, counts, group=self.group)
-        return counts.tolist(), recv.tolist()
-
-    def _forward_exact(self, x, mark):
-        T, d = x.shape
-        ids, coef = self.route_fn(x)
-        mark("route")
-        order, send_ids, counts = self.plan(ids)
-        send_rows = x.index_select(0, torch.div(order, self.A, rounding_mode="floor"))
-        mark("plan+gather")
-        out_c, in_c = self._exchange_counts(counts.reshape(-1, 1))
-        out_splits, in_splits = [c[0] for c in out_c], [c[0] for c in in_c]
-        mark("counts")
-        n_recv = int(sum(in_splits))
-        recv_rows = x.new_empty((n_recv, d))
-        recv_ids = send_ids.new_empty((n_recv,))
-        dist.all_to_all_single(recv_rows, send_rows, in_splits, out_splits, group=self.group)
-        dist.all_to_all_single(recv_ids, send_ids, in_splits, out_splits, group=self.group)
-        mark("dispatch")
-        partial = self.experts_fn(recv_rows, recv_ids, None) if n_recv else torch.empty((0, d), dtype=torch.float32, device=x.device)
-        mark("experts")
-        back = torch.empty((T * self.A, d), dtype=torch.float32, device=x.device)
-        dist.all_to_all_single(back, partial, out_splits, in_splits, group=self.group)
-        mark("combine all-to-all")
-        pos = torch.empty_like(order)
-        pos[order] = torch.arange(order.numel(), device=order.device)  # slot t * A + a came back as row pos[t * A + a]
-        self.last = dict(ids=ids, coef=coef, sent=out_splits, received=in_splits)
-        y = self.reduce_fn(back, pos.reshape(T, self.A), ids, coef, None)
-        mark("reduce")
-        return y
-
-    def _forward_dedup(self, x, mark):
-        T, d = x.shape
-        dev = x.device
-        W, A = self.world, self.A
-        ids, coef = self.route_fn(x)
-        mark("route")
-        order, send_ids, slot_counts = self.plan(ids)  # slots by destination, (token, slot) order inside a destination
-        S = order.numel()
-        tok = torch.div(order, A, rounding_mode="floor")
-        dest = torch.repeat_interleave(torch.arange(W, device=dev), slot_counts, output_size=S)
-        # pairs (destination, token): a new pair starts where either changes along the sorted slots
-        new_pair = torch.ones(S, dtype=torch.bool, device=dev)
-        new_pair[1:] = (tok[1:] != tok[:-1]) | (dest[1:] != dest[:-1])
-        pair_of_slot = torch.cumsum(new_pair.to(torch.int64), 0) - 1          # global pair index of every sorted slot
-        first = torch.nonzero(new_pair).reshape(-1)                           # first sorted slot of every pair
-        pair_tok, pair_dest = tok[first], dest[first]
-        pair_counts = torch.bincount(pair_dest, minlength=W)
-        pair_start = torch.cumsum(pair_counts, 0) - pair_counts               # first pair of every destination
-        send_rows = x.index_select(0, pair_tok)
-        send_rel = (pair_of_slot - pair_start[dest]).to(torch.int32)           # the slot's row inside its destination's block
-        send_coef = coef.reshape(-1)[order]
-        mark("plan+gather")
-        out_c, in_c = self._exchange_counts(torch.stack([slot_counts, pair_counts], 1))
-        out_slots, out_pairs = [c[0] for c in out_c], [c[1] for c in out_c]
-        in_slots, in_pairs = [c[0] for c in in_c], [c[1] for c in in_c]
-        mark("counts")
-        n_slots, n_pairs = int(sum(in_slots)), int(sum(in_pairs))
-        recv_rows = x.new_empty((n_pairs, d))
-        # one message per slot: local expert id, row inside the destination's block, coefficient (bits)
-        send_meta = torch.stack([send_ids, send_rel, send_coef.view(torch.int32)], 1).contiguous()
-        recv_meta = send_meta.new_empty((n_slots, 3))
-        dist.all_to_all_single(recv_rows, send_rows, in_pairs, out_pairs, group=self.group)
-        dist.all_to_all_single(recv_meta, send_meta, in_slots, out_slots, group=self.group)
-        recv_ids, recv_rel, recv_coef = recv_meta[:, 0].contiguous(), recv_meta[:, 1], recv_meta[:, 2].contiguous().view(torch.float32)
-        mark("dispatch")
-        # the slot's row among everything received: its source's first row + its row inside the source's block
-        in_slots_t, in_pairs_t = torch.tensor(in_slots, device=dev), torch.tensor(in_pairs, device=dev)
-        src = torch.repeat_interleave(torch.arange(W, device=dev), in_slots_t, output_size=n_slots)
-        row_index = (recv_rel.to(torch.int64) + (torch.cumsum(in_pairs_t, 0) - in_pairs_t)[src])
-        if n_slots:
-            partial = self.experts_fn(recv_rows, recv_ids, row_index.to(torch.int32))
-        else:
-            partial = torch.empty((0, d), dtype=torch.float32, device=dev)
-        mark("experts")
-        # expert-side sum per received row: its slots are consecutive (the source sorted them); a table [rows, k + 1] of slot
-        # positions, padded with coefficient 0 on a valid row, feeds the ordered weighted sum
-        if n_pairs:
-            start = torch.ones(n_slots, dtype=torch.bool, device=dev)
-            start[1:] = row_index[1:] != row_index[:-1]
-            first_slot = torch.nonzero(start).reshape(-1)                       # one per received row, in row order
-            rank_in_row = torch.arange(n_slots, device=dev) - first_slot[row_index]
-            pos_t = torch.zeros((n_pairs, A), dtype=torch.int64, device=dev)
-            coef_t = torch.zeros((n_pairs, A), dtype=torch.float32, device=dev)
-            ids_t = torch.zeros((n_pairs, A), dtype=torch.int32, device=dev)
-            pos_t[row_index, rank_in_row] = torch.arange(n_slots, device=dev)
-            coef_t[row_index, rank_in_row] = recv_coef
-            ids_t[row_index, rank_in_row] = torch.where(recv_ids < 0, recv_ids, torch.zeros_like(recv_ids))  # invalid ids poison the row
-            summed = self.reduce_fn(partial, pos_t, ids_t, coef_t, torch.float32)
-        else:
-            summed = torch.empty((0, d), dtype=torch.float32, device=dev)
-        mark("expert-side sum")
-        back = torch.empty((int(sum(out_pairs)), d), dtype=torch.float32, device=dev)
-        dist.all_to_all_single(back, summed, out_pairs, in_pairs, group=self.group)
-        mark("combine all-to-all")
-        # home: token t's rows, one per rank that served it, added in ascending rank order
-        pos_h = torch.zeros((T, W), dtype=torch.int64, device=dev)
-        coef_h = torch.zeros((T, W), dtype=torch.float32, device=dev)
-        pos_h[pair_tok, pair_dest] = torch.arange(pair_tok.numel(), device=dev)
-        coef_h[pair_tok, pair_dest] = 1.0
-        ids_h = torch.zeros((T, W), dtype=torch.int32, device=dev)
-        self.last = dict(ids=ids, coef=coef, sent=out_slots, received=in_slots, rows_sent=out_pairs, rows_received=in_pairs)
-        y = self.reduce_fn(back, pos_h, ids_h, coef_h, None)
-        mark("reduce")
-        return y
+def meta_ints(Cr, Cs):
+    """int32 words of one (source, destination) metadata block for capacities of Cr rows and Cs slots."""
+    return 4 + 2 * Cr + 3 * Cs
 
 
-def cuda_layer(d, I, E, k, act, router_w, router_bias, gate_up_local, down_local, world, rank, max_local_tokens, capacity=None, group=None,
-               math=2, dedup=True):
-    """The expert-parallel layer on this rank's GPU. router_w: BF16 or FP32 [E + 1, d] (row E gates the shared expert),
-    replicated. gate_up_local / down_local: this rank's E / world routed experts followed by the shared expert
-    ([(E / world + 1) * 2I, d] and [(E / world + 1) * d, I], uniform 4-bit). capacity: the most slots this rank accepts in
-    one forward (default: every slot of every rank, the worst case)."""
-    from . import kernels as K
-    from .layer import MoeLayer
-
-    El, A = E // world, k + 1
-    cap = capacity if capacity is not None else world * max_local_tokens * A
-    dummy_router = torch.zeros((El, d), dtype=torch.float32, device=router_w.device)
-    shard = MoeLayer(d, I, El, 1, act, dummy_router, gate_up_local, down_local, shared="stacked", shared_coef="one", max_tokens=(cap + 1) // 2,
-                     grouped_min_tokens=1, math=math)
-    R = E + 1
-
-    def route(x):
-        T = x.shape[0]
-        logits = torch.empty((T, R), dtype=torch.float32, device=x.device)
-        if router_w.dtype == torch.bfloat16:
-            K.linear_bf16w(x, router_w, logits, T, R, d, act, K.Act.F32)
-        else:
-            K.linear_f32w(x, router_w, logits, T, R, d, act, K.Act.F32)
-        if router_bias is not None:
-            logits[:, :E] += router_bias
-        ids = torch.empty((T, A), dtype=torch.int32, device=x.device)
-        coef = torch.empty((T, A), dtype=torch.float32, device=x.device)
-        err = K.new_err(x.device)
-        K.moe_router(logits, R, T, E, k, logits[:, E:], R, E, ids, coef, K.Act.F32, err)
-        return ids, coef
-
-    def experts(rows, local_ids, row_index):
-        return shard.experts_partial(rows, local_ids, row_index=row_index)
-
-    def reduce(partial, pos, ids, coef, out_dtype):
-        T, Wd = ids.shape
-        out_act = K.Act.F32 if out_dtype == torch.float32 else act
-        y = torch.empty((T, d), dtype=K._dtype(out_act), device=partial.device)
-        K.moe_combine_reduce(partial, ids.contiguous(), coef.contiguous(), T, Wd, E + 1, d, y, out_act, pos=pos.contiguous())
-        return y
-
-    ep = ExpertParallelMoe(E, k, world, rank, route, experts, reduce, group=group, dedup=dedup)
-    ep.shard = shard
-    return ep
-
-
-def shard_stack(full, E, world, rank):
-    """This rank's slice of a full stacked weight [(E + 1) * N, K] (kernels.QWeight): its E / world routed experts followed
-    by the shared expert (expert E), as a new QWeight."""
-    from . import kernels as K
-
-    N = full.N // (E + 1)
+def placement(E, world, bias=None, k=10, balanced=True, seed=1234, sigma=0.82):
+    """owner[e] and local_of[e] for the E routed experts (E % world == 0; every rank holds E / world of them) plus entry E for
+    the stacked shared expert (local index E / world on every rank). balanced: experts are dealt in order of an estimated load
+    - the share of top-k picks each gets from logits N(0, sigma) + bias, sampled with a fixed seed - always to the rank with
+    the least load so far that still has room; else contiguous blocks e -> e // (E / world). Returns a dict of numpy arrays."""
+    if E % world != 0:
+        raise ValueError("placement: %d experts do not divide over %d ranks" % (E, world))
     El = E // world
+    owner = np.zeros(E + 1, np.int32)
+    local_of = np.zeros(E + 1, np.int32)
+    if balanced and world > 1 and bias is not None:
+        rng = np.random.default_rng(seed)
+        logits = rng.standard_normal((4096, E)).astype(np.float32) * sigma + np.asarray(bias, np.float32)[None, :]
+        picks = np.argpartition(-logits, k - 1, axis=1)[:, :k]
+        load = np.bincount(picks.reshape(-1), minlength=E).astype(np.float64) + 1e-3
+        order = np.lexsort((np.arange(E), -load))  # descending load, ties by index
+        rank_load, room = np.zeros(world), np.full(world, El)
+        for e in order:
+            cand = [r for r in range(world) if room[r] > 0]
+            r = min(cand, key=lambda q: (rank_load[q], q))
+            owner[e] = r
+            rank_load[r] += load[e]
+            room[r] -= 1
+    else:
+        owner[:E] = np.arange(E) // El
+    experts_of = [np.nonzero(owner[:E] == r)[0].astype(np.int64) for r in range(world)]
+    for r in range(world):
+        local_of[experts_of[r]] = np.arange(El, dtype=np.int32)
+    owner[E], local_of[E] = -1, El  # the shared expert: every rank's own
+    return dict(owner=owner, local_of=local_of, experts_of=experts_of, El=El)
+
+
+def plan_reference(ids, coef, E, owner, local_of, P, rank, Cr, Cs):
+    """The layout strix_ep_plan writes, restated in numpy (the definition the kernel is tested against):
+    rowtok [P, Cr], meta [P, MW], pos [T, P], flags [2]."""
+    T, A = ids.shape
+    MW = meta_ints(Cr, Cs)
+    rowtok = np.zeros((P, Cr), np.int32)
+    meta = np.zeros((P, MW), np.int32)
+    pos = np.full((T, P), -1, np.int32)
+    n_rows, n_slots = np.zeros(P, np.int64), np.zeros(P, np.int64)
+    cb = np.ascontiguousarray(coef, np.float32).view(np.int32)
+    for t in range(T):
+        row_of = {}
+        for a in range(A):
+            e = int(ids[t, a])
+            if 0 <= e <= E:
+                r = rank if e == E else int(owner[e])
+                loc = int(local_of[e])
+            else:
+                r, loc = rank, -1
+            if r not in row_of:
+                row_of[r] = int(n_rows[r])
+                n_rows[r] += 1
+                if row_of[r] < Cr:
+                    rowtok[r, row_of[r]] = t
+                    meta[r, 4 + 2 * row_of[r]] = n_slots[r]
+            j = int(n_slots[r])
+            n_slots[r] += 1
+            if j < Cs and row_of[r] < Cr:
+                meta[r, 4 + 2 * Cr + 3 * j: 4 + 2 * Cr + 3 * j + 3] = (loc, row_of[r], cb[t, a])
+                meta[r, 4 + 2 * row_of[r] + 1] += 1
+        for r, i in row_of.items():
+            pos[t, r] = i if i < Cr else -1
+    flags = np.zeros(2, np.uint32)
+    for r in range(P):
+        meta[r, 0], meta[r, 1] = min(n_rows[r], Cr), min(n_slots[r], Cs)
+        if n_rows[r] > Cr:
+            flags[0] = max(flags[0], n_rows[r])
+        if n_slots[r] > Cs:
+            flags[1] = max(flags[1], n_slots[r])
+    return rowtok, meta, pos, flags
+
+
+class ExpertParallelMoe:
+    """The exchange logic over a backend. backend methods, per chunk c (buffers are the backend's, reused every step):
+      route(c, x) -> (ids [T, A], coef [T, A]);  plan(c) -> (rows_send [P, Cr, d], meta_send [P, MW]);
+      experts(c, rows_recv, meta_recv) -> summed [P, Cr, d] float32;  home(c, back) -> y [T, d]
+    and recv buffers rows_recv(c), meta_recv(c), back(c)."""
+
+    def __init__(self, world, rank, backend, group=None, chunks=1, timeout_s=None):
+        self.world, self.rank, self.backend, self.group, self.chunks = world, rank, backend, group, chunks
+        self.timeout_s = timeout_s
+
+    def _a2a(self, out, inp):
+        if self.world == 1:
+            return inp
+        w = dist.all_to_all_single(out, inp, group=self.group, async_op=self.timeout_s is not None)
+        if w is not None and not w.wait(timeout=__import__("datetime").timedelta(seconds=self.timeout_s)):
+            raise RuntimeError("expert-parallel exchange: a peer did not join within %.1f s" % self.timeout_s)
+        return out
+
+    def forward(self, x):
+        """y [T, d] for this rank's tokens x [T, d] (T a multiple of the chunk count)."""
+        b, n = self.backend, self.chunks
+        T = x.shape[0]
+        if T % n != 0:
+            raise ValueError("ExpertParallelMoe: %d tokens do not split into %d chunks" % (T, n))
+        Tc = T // n
+        b.begin(x)
+        recv = [None] * n
+        for c in range(n):
+            with b.stream(c):
+                b.route(c, x[c * Tc:(c + 1) * Tc])
+                rows_send, meta_send = b.plan(c)
+                recv[c] = (self._a2a(b.rows_recv(c), rows_send), self._a2a(b.meta_recv(c), meta_send))
+        back = [None] * n
+        for c in range(n):
+            with b.stream(c):
+                summed = b.experts(c, *recv[c])
+                back[c] = self._a2a(b.back(c), summed)
+        ys = []
+        for c in range(n):
+            with b.stream(c):
+                ys.append(b.home(c, back[c]))
+        return b.end(ys)
+
+
+class _NoStream:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        return False
+
+
+class CudaBackend:
+    """The compute steps on this rank's GPU, over this library's kernels. router_w: BF16 or FP32 [E + 1, d] (row E gates the
+    shared expert), replicated. gate_up_local / down_local: this rank's E / world routed experts in placement order followed by
+    the shared expert (uniform 4-bit stacks)."""
+
+    def __init__(self, d, I, E, k, act, router_w, router_bias, gate_up_local, down_local, world, rank, place, max_local_tokens, chunks=1, math=2,
+                 slot_capacity=None):
+        from . import kernels as K
+        from ._lib import lib
+        from .layer import MoeLayer
+
+        self.K, self.lib = K, lib
+        self.d, self.I, self.E, self.k, self.A, self.act = d, I, E, k, k + 1, K.Act(act)
+        self.P, self.rank, self.El = world, rank, E // world
+        self.router_w, self.router_bias = router_w, router_bias
+        dev = router_w.device
+        self.dev = dev
+        self.chunks = chunks
+        if max_local_tokens % chunks != 0:
+            raise ValueError("CudaBackend: %d tokens do not split into %d chunks" % (max_local_tokens, chunks))
+        Tc = max_local_tokens // chunks
+        self.Tc = Tc
+        self.Cr = Tc  # a token sends at most one row to a rank
+        if slot_capacity is None:  # 2.5 x the even share of a chunk's slots, or all of them on one or two ranks
+            slot_capacity = Tc * self.A if world <= 2 else min(Tc * self.A, int(2.5 * Tc * self.A / world) + 1024)
+        self.Cs = int(slot_capacity)
+        self.MW = meta_ints(self.Cr, self.Cs)
+        self.owner = torch.from_numpy(place["owner"].copy()).to(dev)
+        self.local_of = torch.from_numpy(place["local_of"].copy()).to(dev)
+        n_cap = world * self.Cs
+        dummy_router = torch.zeros((self.El, d), dtype=torch.float32, device=dev)
+        self.streams = [torch.cuda.Stream(device=dev) for _ in range(chunks)] if chunks > 1 else [None]
+        adt = K._dtype(self.act)
+        self.c = []
+        for _ in range(chunks):
+            shard = MoeLayer(d, I, self.El, 1, act, dummy_router, gate_up_local, down_local, shared="stacked", shared_coef="one", max_tokens=(n_cap + 1) // 2,
+                             grouped_min_tokens=1, math=math)
+            z = lambda *s, dt=torch.int32: torch.zeros(s, dtype=dt, device=dev)  # noqa: E731
+            self.c.append(dict(
+                shard=shard, logits=z(Tc, E + 1, dt=torch.float32), ids=z(Tc, self.A), coef=z(Tc, self.A, dt=torch.float32), err=K.new_err(dev),
+                rowtok=z(world, self.Cr), meta_send=z(world, self.MW), meta_recv=z(world, self.MW), pos=z(Tc, world), flags=z(2),
+                rows_send=z(world, self.Cr, d, dt=adt), rows_recv=z(world, self.Cr, d, dt=adt), slot_ids=z(n_cap), slot_row=z(n_cap),
+                partial=torch.empty((n_cap, d), dtype=torch.float32, device=dev), summed=z(world, self.Cr, d, dt=torch.float32),
+                back=z(world, self.Cr, d, dt=torch.float32), y=torch.empty((Tc, d), dtype=adt, device=dev)))
+        self.launches = 0
+
+    # ---- the driver's hooks -------------------------------------------------------------------------------------------------
+    def stream(self, c):
+        return torch.cuda.stream(self.streams[c]) if self.streams[c] is not None else _NoStream()
+
+    def _sp(self, c):
+        return self.K._s(self.streams[c])
+
+    def begin(self, x):
+        self.launches = 0
+        if self.chunks > 1:
+            cur = torch.cuda.current_stream(self.dev)
+            for s in self.streams:
+                s.wait_stream(cur)
+
+    def end(self, ys):
+        if self.chunks > 1:
+            cur = torch.cuda.current_stream(self.dev)
+            for s in self.streams:
+                cur.wait_stream(s)
+        return ys[0] if len(ys) == 1 else torch.cat(ys, 0)
+
+    def rows_recv(self, c):
+        return self.c[c]["rows_recv"]
+
+    def meta_recv(self, c):
+        return self.c[c]["meta_recv"]
+
+    def back(self, c):
+        return self.c[c]["back"]
+
+    def route(self, c, x):
+        K, b, st = self.K, self.c[c], self.streams[c]
+        T, R = x.shape[0], self.E + 1
+        b["x"] = x
+        if self.router_w.dtype == torch.bfloat16:
+            K.linear_bf16w(x, self.router_w, b["logits"], T, R, self.d, self.act, K.Act.F32, stream=st)
+        else:
+            K.linear_f32w(x, self.router_w, b["logits"], T, R, self.d, self.act, K.Act.F32, stream=st)
+        if self.router_bias is not None:
+            b["logits"][:, : self.E] += self.router_bias
+        K.moe_router(b["logits"], R, T, self.E, self.k, b["logits"][:, self.E:], R, self.E, b["ids"], b["coef"], K.Act.F32, b["err"], stream=st)
+        self.launches += 2
+
+    def plan(self, c):
+        from ._lib import call
+
+        K, b = self.K, self.c[c]
+        T = b["x"].shape[0]
+        call("strix_ep_plan", K._p(b["ids"]), K._p(b["coef"]), T, self.A, self.E, K._p(self.owner), K._p(self.local_of), self.P, self.rank, self.Cr, self.Cs,
+             K._p(b["rowtok"]), K._p(b["meta_send"]), K._p(b["pos"]), K._p(b["flags"]), self._sp(c))
+        call("strix_ep_gather_rows", K._p(b["x"]), self.d, int(self.act), K._p(b["rowtok"]), K._p(b["meta_send"]), self.P, self.Cr, self.Cs, K._p(b["rows_send"]),
+             self._sp(c))
+        self.launches += 2
+        return b["rows_send"], b["meta_send"]
+
+    def experts(self, c, rows_recv, meta_recv):
+        from ._lib import call
+
+        K, b = self.K, self.c[c]
+        b["meta_last"] = meta_recv
+        call("strix_ep_unpack", K._p(meta_recv), self.P, self.Cr, self.Cs, K._p(b["slot_ids"]), K._p(b["slot_row"]), self._sp(c))
+        b["shard"].experts_partial(rows_recv.reshape(-1, self.d), b["slot_ids"], partial=b["partial"], stream=self.streams[c], row_index=b["slot_row"])
+        call("strix_ep_row_sum", K._p(b["partial"]), K._p(meta_recv), self.P, self.Cr, self.Cs, self.d, K._p(b["summed"]), self._sp(c))
+        self.launches += 9  # unpack, grouping (3), tiles, ordered rows, two FFN kernels, row sum
+        return b["summed"]
+
+    def home(self, c, back):
+        from ._lib import call
+
+        K, b = self.K, self.c[c]
+        T = b["x"].shape[0]
+        call("strix_ep_home_sum", K._p(back), K._p(b["pos"]), K._p(b["ids"]), T, self.A, self.E, self.P, self.Cr, self.d, K._p(b["y"][:T]), int(self.act), self._sp(c))
+        self.launches += 1
+        return b["y"][:T]
+
+    # ---- after a step ---------------------------------------------------------------------------------------------------------
+    def check(self):
+        """Raises if a step overflowed a capacity, a router or expert error word is set, or a tensor-core wait was given up."""
+        from ._lib import StrixError
+
+        for i, b in enumerate(self.c):
+            f = b["flags"].cpu().numpy().view(np.uint32)
+            if f[0] or f[1]:
+                raise StrixError("expert-parallel exchange overflowed its fixed capacity in chunk %d: %d rows (capacity %d), %d slots (capacity %d) "
+                                 "for one destination; raise slot_capacity" % (i, f[0], self.Cr, f[1], self.Cs))
+            self.K.check_router_error(b["err"], "expert-parallel router")
+            e = b["shard"].probe("err", 1).cpu().numpy()
+            if e[3]:
+                raise StrixError("expert-parallel experts: error words %s" % e[3:6].tolist())
+
+    def received_slots(self):
+        return float(sum(int(b["meta_last"][:, 1].sum().item()) for b in self.c if "meta_last" in b))
+
+
+class CudaLayer:
+    """ExpertParallelMoe over a CudaBackend: the object bench.py and the GPU tests use."""
+
+    def __init__(self, backend, world, rank, group=None):
+        self.backend, self.chunks = backend, backend.chunks
+        self.ep = ExpertParallelMoe(world, rank, backend, group=group, chunks=backend.chunks)
+
+    def forward(self, x):
+        return self.ep.forward(x)
+
+    def check(self):
+        self.backend.check()
+
+    def received_slots(self):
+        return self.backend.received_slots()
+
+    def launches_per_step(self):
+        return self.backend.launches
+
+    def last_logits(self):
+        return torch.cat([b["logits"] for b in self.backend.c], 0)
+
+    def last_ids(self):
+        return torch.cat([b["ids"] for b in self.backend.c], 0)
+
+
+def cuda_layer(d, I, E, k, act, router_w, router_bias, gate_up_local, down_local, world, rank, max_local_tokens, placement=None, group=None, math=2, chunks=0,
+               dedup=True, slot_capacity=None):
+    """The expert-parallel layer on this rank's GPU (see CudaBackend). placement: the dict of placement() (default: contiguous).
+    chunks: token chunks per step on separate streams (0 = two when several ranks exchange, else one)."""
+    if not dedup:
+        raise ValueError("cuda_layer: the one-row-per-slot exchange was removed; rows go once per (token, rank)")
+    place = placement if placement is not None else globals()["placement"](E, world, balanced=False)
+    if chunks <= 0:
+        chunks = 2 if world > 1 and max_local_tokens % 2 == 0 else 1
+    be = CudaBackend(d, I, E, k, act, router_w, router_bias, gate_up_local, down_local, world, rank, place, max_local_tokens, chunks=chunks, math=math,
+                     slot_capacity=slot_capacity)
+    return CudaLayer(be, world, rank, group=group)
+
+
+def shard_stack(full, E, world, rank, place=None):
+    """This rank's slice of a full stacked weight [(E + 1) * N, K] (kernels.QWeight): its routed experts in placement order
+    followed by the shared expert (expert E), as a new QWeight."""
+    from . import kernels as K
+
+    place = place if place is not None else placement(E, world, balanced=False)
+    N = full.N // (E + 1)
     rb = K.row_bytes(full.bits, full.K)
-    rows = torch.cat([torch.arange(rank * El * N, (rank + 1) * El * N, device=full.q.device), torch.arange(E * N, (E + 1) * N, device=full.q.device)])
+    dev = full.q.device
+    ex = torch.from_numpy(np.concatenate([place["experts_of"][rank], np.array([E], np.int64)])).to(dev)
+    rows = (ex[:, None] * N + torch.arange(N, device=dev)[None, :]).reshape(-1)
     q = full.q.view(-1, rb).index_select(0, rows).reshape(-1)
     return K.QWeight(full.bits, rows.numel(), full.K, full.G, q, full.scale.index_select(0, rows), full.minv.index_select(0, rows))
