@@ -114,6 +114,16 @@ int strix_linear_q8(const void *x, const strix_qview *w, void *y, int64_t M, int
 /* strixite kernels/linear.hpp:20-26 linear_bf16w: W [N, K] raw BF16 bits (the router projection). */
 int strix_linear_bf16w(const void *x, const uint16_t *w, void *y, int64_t M, int64_t N, int64_t K, int act,
                        int out_act, void *stream);
+/* strixite kernels/linear_wmma.hpp:21-24 linear_q{4,5,6,8}_wmma: the same projections on the tensor cores (tcgen05, FP32
+ * accumulation; activations and dequantized weights as F16 operands, see STRIX_MATH_*). K % 64 == 0. */
+int strix_linear_q4_wmma(const void *x, const strix_qview *w, void *y, int64_t M, int act, int out_act, void *stream);
+int strix_linear_q5_wmma(const void *x, const strix_qview *w, void *y, int64_t M, int act, int out_act, void *stream);
+int strix_linear_q6_wmma(const void *x, const strix_qview *w, void *y, int64_t M, int act, int out_act, void *stream);
+int strix_linear_q8_wmma(const void *x, const strix_qview *w, void *y, int64_t M, int act, int out_act, void *stream);
+/* strixite kernels/linear_wmma.hpp:27-29 linear_bf16w_wmma: BF16 tokens, BF16 weights, FP32 outputs on the tensor cores
+ * (both operands by TMA; products exact, only the summation order differs from linear_bf16w). K % 64 == 0. */
+int strix_linear_bf16w_wmma(const void *x, const uint16_t *w, void *y, int64_t M, int64_t N, int64_t K, int act,
+                            int out_act, void *stream);
 /* The same with FP32 weights [N, K] (a router kept in FP32). No counterpart in the reference. */
 int strix_linear_f32w(const void *x, const float *w, void *y, int64_t M, int64_t N, int64_t K, int act, int out_act,
                       void *stream);
@@ -126,6 +136,26 @@ int strix_swiglu(const void *gu, void *h, int64_t rows, int64_t I, int act, void
 int strix_residual_add(void *x, const void *y, int64_t n, int act, void *stream);
 /* strixite kernels/hc.hpp:52-55 hc_inject: x[t, s*N + n] = fma(w_in[t, s], y[t, n], x[t, s*N + n]), x [M, H*N]. */
 int strix_hc_inject(void *x, const void *y, const float *w_in, int64_t M, int64_t N, int64_t H, int act, void *stream);
+
+/* ---- the hyper-connection bracket around the MoE sublayer ------------------------------------------------------ */
+
+/* strixite kernels/hc.hpp:36-39 hc_mix_down (the Q4 and Q8 overloads; `bits` 4 or 8): X [T, H*d] -> h [T, r] =
+ * silu(a / H) for the first r rows of the folded weights w [r (+ H), H*d], w_in [T, H] = 2 sigmoid(a / H) for the next H rows
+ * (when inject; w_in NULL otherwise), inv [T, H] = the per-stream inverse RMS. H == 4, d % 32 == 0, x 16-byte aligned. */
+int strix_hc_mix_down(const void *x, const strix_qview *w, int bits, int64_t T, int64_t H, int64_t d, int64_t r, int inject,
+                      float eps, float *h, float *w_in, float *inv, int act, void *stream);
+/* strixite kernels/hc.hpp:47-50 hc_mix_up: u[t, j] = (1/H) sum_s sigmoid(W_up[s*d + j] . h[t]) * X[t, s*d + j] * inv[t, s] *
+ * (1 + norm_w[s*d + j]). w_up [H*d, r] is CHUNK-major (strixite formats/q4.hpp:41-55: 32-code chunk c of row n at
+ * q[(c*N + n) * chunk bytes], group g's scale / min at [g*N + n]); r % 32 == 0, r <= 1024. u [T, d] in the activation dtype. */
+int strix_hc_mix_up(const float *h, const strix_qview *w_up, int bits, const void *x, const float *norm_w, const float *inv,
+                    int64_t T, int64_t H, int64_t d, void *u, int act, void *stream);
+/* strixite kernels/hc_wmma.hpp:38-42 hc_inject_inv: hc_inject (X[t, s*d + j] += w_in[t, s] * y[t, j], one rounding) and the
+ * inverse RMS of the updated, stored streams into inv [T, H], in one pass. X is bit-identical to strix_hc_inject's. */
+int strix_hc_inject_inv(void *x, const float *w_in, const void *y, int64_t T, int64_t H, int64_t d, float eps, float *inv,
+                        int act, void *stream);
+/* strixite formats/q4.hpp:55 to_chunk_major (and the Q8 twin): host arrays, row-major -> chunk-major. */
+int strix_to_chunk_major(int bits, const uint8_t *q, const uint16_t *scale, const uint16_t *minv, int64_t N, int64_t K,
+                         int64_t G, uint8_t *q_out, uint16_t *scale_out, uint16_t *min_out);
 
 /* ---- experts, per slot (decode / verify) ---------------------------------------------------------------------- */
 
@@ -199,6 +229,10 @@ int strix_linear_q4_experts_combine_grouped_fixed(const void *h, const strix_qvi
 /* Number of thread blocks of the tensor-core grouped GEMM that abandoned a bounded wait since the library was loaded:
  * 0 in a healthy run (their outputs are undefined otherwise). No counterpart in the reference. Synchronizes. */
 unsigned int strix_umma_abort_count(void);
+/* Launches of the grouped kernels that stored nothing because the workspace they were given had been grouped for another
+ * (M * A, E) than the call stated (same byte size, other contents): the caller's outputs are untouched. 0 in a healthy run.
+ * No counterpart in the reference (its kernels trust the workspace header). Synchronizes. */
+unsigned int strix_workspace_refusal_count(void);
 /* Diagnostics of the many-token tensor-core kernels: clock cycles their warp roles spent waiting on each other, summed
  * over thread blocks since the last reset; out32 = 2 kernels x 16 counters (index list in csrc/prefill_umma.cu).
  * No counterpart in the reference. Synchronizes. */

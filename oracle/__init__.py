@@ -126,6 +126,16 @@ def ref_quantize(bits, w, G):
     return qw
 
 
+def ref_to_chunk_major(w):
+    """The reference's own to_chunk_major (formats/q4.cpp:101-119, formats/q8.cpp) through oracle/_ref."""
+    q, sc, mn = np.empty_like(w.q), np.empty_like(w.scale), np.empty_like(w.minv)
+    rc = ref.ref_to_chunk_major(_int(w.bits), _p(w.q), _p(w.scale), _p(w.minv), _i64(w.N), _i64(w.K), _i64(w.G), _p(q),
+                                _p(sc), _p(mn))
+    if rc != 0:
+        raise RuntimeError(ref.ref_last_error().decode())
+    return QWeight(w.bits, w.N, w.K, w.G, q, sc, mn)
+
+
 def dequantize(qw, lib=None, fn="orc_dequantize"):
     out = np.empty((qw.N, qw.K), np.float32)
     rc = getattr(lib or orc, fn)(_int(qw.bits), _p(qw.q), _p(qw.scale), _p(qw.minv), _i64(qw.N), _i64(qw.K), _i64(qw.G), _p(out))
@@ -296,6 +306,39 @@ def moe_shared_add_inject(y, s, gate_logit, gate_col, gate_index, x, w_in, err=N
 def hc_inject(x, y, w_in):
     M, N = y.shape
     orc.orc_hc_inject(_p(x), _p(y), _p(w_in), _i64(M), _i64(N), _i64(w_in.shape[1]), _int(act_of(y)))
+
+
+def hc_mix_down(x, w, H, d, r, inject, eps=1e-6):
+    """kernels/hc.hpp:36-39: x [T, H*d] (float32 or bf16 bits), w QWeight [r (+ H), H*d] (4 or 8 bits, folded).
+    Returns (h [T, r], w_in [T, H] or None, inv [T, H]) float32."""
+    T = x.shape[0]
+    assert w.bits in (4, 8) and w.K == H * d and w.N == r + (H if inject else 0)
+    h = np.zeros((T, r), np.float32)
+    w_in = np.zeros((T, H), np.float32) if inject else None
+    inv = np.zeros((T, H), np.float32)
+    orc.orc_hc_mix_down(_p(x), _int(w.bits), _p(w.q), _p(w.scale), _p(w.minv), _i64(w.G), _i64(T), _i64(H), _i64(d),
+                        _i64(r), _int(1 if inject else 0), C.c_float(eps), _p(h), _p(w_in), _p(inv), _int(act_of(x)))
+    return h, w_in, inv
+
+
+def to_chunk_major(w):
+    """formats/q4.hpp:41-55 / formats/q8.hpp:37-46: the chunk-major copy of a 4- or 8-bit QWeight."""
+    assert w.bits in (4, 8) and w.K % 32 == 0
+    q, sc, mn = np.empty_like(w.q), np.empty_like(w.scale), np.empty_like(w.minv)
+    orc.orc_to_chunk_major(_int(w.bits), _p(w.q), _p(w.scale), _p(w.minv), _i64(w.N), _i64(w.K), _i64(w.G), _p(q), _p(sc),
+                           _p(mn))
+    return QWeight(w.bits, w.N, w.K, w.G, q, sc, mn)
+
+
+def hc_mix_up(h, w_up_cm, x, norm_w, inv, H, d):
+    """kernels/hc.hpp:47-50: h [T, r] float32, w_up_cm the CHUNK-major QWeight [H*d, r], x [T, H*d], norm_w [H*d],
+    inv [T, H]. Returns u [T, d] in x's dtype."""
+    T, r = h.shape
+    assert w_up_cm.bits in (4, 8) and w_up_cm.N == H * d and w_up_cm.K == r and r % 32 == 0
+    u = np.zeros((T, d), x.dtype)
+    orc.orc_hc_mix_up(_p(h), _int(w_up_cm.bits), _p(w_up_cm.q), _p(w_up_cm.scale), _p(w_up_cm.minv), _i64(w_up_cm.G),
+                      _i64(r), _p(x), _p(norm_w), _p(inv), _i64(T), _i64(H), _i64(d), _p(u), _int(act_of(x)))
+    return u
 
 
 def residual_add(x, y):

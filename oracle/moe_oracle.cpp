@@ -379,6 +379,82 @@ void orc_hc_inject(void *x, const void *y, const float *w_in, int64_t M, int64_t
             }
 }
 
+// kernels/hc.hip:77-165 hc_mix_down (interface kernels/hc.hpp:29-39). X [T, H*d]; W [r (+ H), H*d] with the hc_norm weight
+// folded in. Per stream s: inv_s = 1 / sqrt(mean(X_s^2) + eps); per row n: a_n = sum_s inv_s * (W_n,s . X_s);
+// h[n] = silu(a_n / H) for n < r, w_in[n - r] = 2 sigmoid(a_n / H) behind them. The dots and the sums of squares are
+// accumulated in double (the kernel: FP32 fma chains over 32-code chunks, s * dot + m * xsum per chunk); the steps after
+// them are the kernel's own FP32 operations in its order.
+void orc_hc_mix_down(const void *x, int bits, const uint8_t *q, const uint16_t *scale, const uint16_t *minv, int64_t G,
+                     int64_t T, int64_t H, int64_t d, int64_t r, int inject, float eps, float *h, float *w_in, float *inv,
+                     int act) {
+    const int64_t K = H * d, R = r + (inject ? H : 0), rb = row_bytes(bits, K);
+    std::vector<float> wrow((size_t)K);
+    for (int64_t t = 0; t < T; ++t) {
+        std::vector<float> iv((size_t)H);
+        for (int64_t s = 0; s < H; ++s) {
+            double sq = 0.0;
+            for (int64_t j = 0; j < d; ++j) {
+                const double v = act_load(x, t * K + s * d + j, act);
+                sq += v * v;
+            }
+            iv[(size_t)s] = 1.0f / std::sqrt((float)sq / (float)d + eps);
+            inv[t * H + s] = iv[(size_t)s];
+        }
+        for (int64_t n = 0; n < R; ++n) {
+            dequant_row(bits, q + n * rb, scale + n * (K / G), minv + n * (K / G), K, G, wrow.data());
+            float a = 0.f;
+            for (int64_t s = 0; s < H; ++s)
+                a = std::fmaf(iv[(size_t)s], (float)dot_row(wrow.data() + s * d, x, t * K + s * d, d, act), a);
+            const float z = a / (float)H;
+            if (n < r) h[t * r + n] = z / (1.0f + std::exp(-z));
+            else w_in[t * H + (n - r)] = 2.0f / (1.0f + std::exp(-z));
+        }
+    }
+}
+
+// formats/q4.cpp:101-119 to_chunk_major (formats/q8.hpp:37-46 for one code per byte): 32-code chunk c of row n moves to
+// [(c * N + n) * chunk bytes], group g's scale / min to [g * N + n]. 4- and 8-bit codes only.
+void orc_to_chunk_major(int bits, const uint8_t *q, const uint16_t *scale, const uint16_t *minv, int64_t N, int64_t K,
+                        int64_t G, uint8_t *q_out, uint16_t *scale_out, uint16_t *min_out) {
+    const int64_t cb = 32 * bits / 8, chunks = K / 32, groups = K / G;
+    for (int64_t n = 0; n < N; ++n) {
+        for (int64_t c = 0; c < chunks; ++c)
+            for (int64_t b = 0; b < cb; ++b) q_out[(c * N + n) * cb + b] = q[(n * chunks + c) * cb + b];
+        for (int64_t g = 0; g < groups; ++g) {
+            scale_out[g * N + n] = scale[n * groups + g];
+            min_out[g * N + n] = minv[n * groups + g];
+        }
+    }
+}
+
+// kernels/hc.hip:176-242 hc_mix_up (interface kernels/hc.hpp:41-50). W_up [H*d, r] CHUNK-major, 4- or 8-bit:
+// u[t, j] = (1/H) sum_s sigmoid(W_up[s*d + j] . h[t]) * (X[t, s*d + j] * inv[t, s] * (1 + norm_w[s*d + j])), rounded once
+// to the activation dtype. The dot accumulates in double; the gate and the combine are the kernel's FP32 steps in order.
+void orc_hc_mix_up(const float *h, int bits, const uint8_t *q, const uint16_t *scale, const uint16_t *minv, int64_t G,
+                   int64_t r, const void *x, const float *norm_w, const float *inv, int64_t T, int64_t H, int64_t d, void *u,
+                   int act) {
+    const int64_t N = H * d, cb = 32 * bits / 8;
+    for (int64_t t = 0; t < T; ++t)
+        for (int64_t j = 0; j < d; ++j) {
+            float sum = 0.f;
+            for (int64_t s = 0; s < H; ++s) {
+                const int64_t row = s * d + j;
+                double acc = 0.0;
+                for (int64_t k = 0; k < r; ++k) {
+                    const uint8_t *chunk = q + ((k / 32) * N + row) * cb;
+                    const int kk = (int)(k % 32);
+                    const int code = bits == 8 ? chunk[kk] : (chunk[kk / 2] >> ((kk & 1) ? 4 : 0)) & 0xF;
+                    const int64_t gi = (k / G) * N + row;
+                    const float w = (float)code * bf16_to_f32(scale[gi]) + bf16_to_f32(minv[gi]);
+                    acc += (double)w * (double)h[t * r + k];
+                }
+                const float z = 1.0f / (1.0f + std::exp(-(float)acc));
+                sum += z * (act_load(x, t * N + row, act) * inv[t * H + s] * (1.0f + norm_w[row]));
+            }
+            act_store(u, t * d + j, sum / (float)H, act);
+        }
+}
+
 // kernels/moe_router.hip:154-180 - defined as moe_shared_add then hc_inject on the stored y.
 void orc_moe_shared_add_inject(void *y, const void *s, const float *gate_logit, int64_t gate_ld, int64_t M, int64_t N,
                                uint32_t gate_index, void *x, const float *w_in, int64_t H, int act, uint32_t *err) {

@@ -89,4 +89,21 @@ int ref_q4_from_q8(const uint8_t *q, const uint16_t *scale, const uint16_t *minv
     }
 }
 
+// formats/q4.hpp:55 / formats/q8.hpp:46 to_chunk_major: the reference's own row-major -> chunk-major conversion.
+int ref_to_chunk_major(int bits, const uint8_t *q, const uint16_t *scale, const uint16_t *minv, int64_t N, int64_t K,
+                       int64_t G, uint8_t *q_out, uint16_t *scale_out, uint16_t *min_out) {
+    try {
+        if (bits == 4) copy_out(strix::to_chunk_major(make<strix::Q4Weight>(q, scale, minv, N, K, G, K / 2), "ref_to_chunk_major"), q_out, scale_out, min_out);
+        else if (bits == 8) copy_out(strix::to_chunk_major(make<strix::Q8Weight>(q, scale, minv, N, K, G, K), "ref_to_chunk_major"), q_out, scale_out, min_out);
+        else {
+            g_msg = "ref_to_chunk_major: bits must be 4 or 8";
+            return 2;
+        }
+        return 0;
+    } catch (const std::exception &e) {
+        g_msg = e.what();
+        return 1;
+    }
+}
+
 }  // extern "C"

@@ -58,10 +58,19 @@ SIGNATURES = {
     "strix_linear_q6": [_vp, _qv, _vp, _i64, _int, _int, _vp],
     "strix_linear_q8": [_vp, _qv, _vp, _i64, _int, _int, _vp],
     "strix_linear_bf16w": [_vp, _vp, _vp, _i64, _i64, _i64, _int, _int, _vp],
+    "strix_linear_q4_wmma": [_vp, _qv, _vp, _i64, _int, _int, _vp],
+    "strix_linear_q5_wmma": [_vp, _qv, _vp, _i64, _int, _int, _vp],
+    "strix_linear_q6_wmma": [_vp, _qv, _vp, _i64, _int, _int, _vp],
+    "strix_linear_q8_wmma": [_vp, _qv, _vp, _i64, _int, _int, _vp],
+    "strix_linear_bf16w_wmma": [_vp, _vp, _vp, _i64, _i64, _i64, _int, _int, _vp],
     "strix_linear_f32w": [_vp, _vp, _vp, _i64, _i64, _i64, _int, _int, _vp],
     "strix_swiglu": [_vp, _vp, _i64, _i64, _int, _vp],
     "strix_residual_add": [_vp, _vp, _i64, _int, _vp],
     "strix_hc_inject": [_vp, _vp, _vp, _i64, _i64, _i64, _int, _vp],
+    "strix_hc_mix_down": [_vp, _qv, _int, _i64, _i64, _i64, _i64, _int, C.c_float, _vp, _vp, _vp, _int, _vp],
+    "strix_hc_mix_up": [_vp, _qv, _int, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _int, _vp],
+    "strix_hc_inject_inv": [_vp, _vp, _vp, _i64, _i64, _i64, C.c_float, _vp, _int, _vp],
+    "strix_to_chunk_major": [_int, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp],
     "strix_linear_q4_experts_gather": [_vp, _qv, _i64, _vp, _i64, _i64, _vp, _int, _vp, _vp],
     "strix_linear_q4_experts_combine": [_vp, _qv, _i64, _vp, _vp, _i64, _i64, _vp, _int, _vp, _vp],
     "strix_linear_q4_experts_gather_swiglu": [_vp, _qv, _i64, _vp, _i64, _i64, _vp, _int, _vp, _vp],
@@ -91,6 +100,7 @@ SIGNATURES = {
     "strix_ep_home_sum": [_vp, _vp, _vp, _i64, _i64, _i64, _int, _i64, _i64, _vp, _int, _vp],
     "strix_hash64": [_vp, _sz],
     "strix_umma_abort_count": [],
+    "strix_workspace_refusal_count": [],
     "strix_umma_wait_cycles": [_vp, _int],
     "strix_last_error": [],
     "strix_version": [],
@@ -100,6 +110,7 @@ _RESTYPES = {
     "strix_ep_meta_ints": _i64,
     "strix_hash64": C.c_uint64,
     "strix_umma_abort_count": C.c_uint,
+    "strix_workspace_refusal_count": C.c_uint,
     "strix_umma_wait_cycles": None,
     "strix_moe_route_workspace_bytes": _sz,
     "strix_last_error": C.c_char_p,

@@ -237,14 +237,17 @@ __global__ void __launch_bounds__(kSegWarps * 32) route_place_kernel(const int32
     }
 }
 
+__device__ unsigned int g_ws_refusals = 0;  // launches refused over a workspace grouped for other sizes (strix_workspace_refusal_count)
+
 // FP32 path: one tile (up to 16 slots of one expert) x 8 output rows per block, a warp per row. The row's codes are
 // decoded once per 32-code chunk and applied to every slot of the tile. COMBINE: inputs h[slot], outputs the per-slot
 // dots into `partial` (FP32); else inputs x[slot / A], outputs y[slot] in the activation dtype.
 template <typename T, bool COMBINE>
 __global__ void __launch_bounds__(256)
-    grouped_f32_kernel(const T *x, StackView w, const int32_t *ws, int64_t A, T *y, float *partial) {
+    grouped_f32_kernel(const T *x, StackView w, const int32_t *ws, int64_t A, T *y, float *partial, int32_t S, int32_t E) {
     constexpr int R = 16;
-    const int32_t n_tiles = ws[0], S = ws[1], E = ws[2];
+    if (!sb::ws_is_for(ws, S, E, &g_ws_refusals)) return;
+    const int32_t n_tiles = ws[0];
     const int tile = blockIdx.y;
     if (tile >= n_tiles) return;
     const sb::RouteTables rt = sb::route_tables(ws, S, E);
@@ -417,15 +420,15 @@ int gather_grouped(const char *fn, const void *x, const StackView &w, int64_t E,
     auto st = static_cast<cudaStream_t>(stream);
     const auto *wsi = static_cast<const int32_t *>(ws);
     if (math != STRIX_MATH_F32) {
-        SB_TRY(grouped_umma(fn, x, w, wsi, M, A, y, nullptr, act, /*combine=*/false, st));
+        SB_TRY(grouped_umma(fn, x, w, wsi, M, A, E, y, nullptr, act, /*combine=*/false, st));
         return 0;
     }
     // tiles that can exist: S / 16 full ones + one ragged tile per non-empty bucket (at most S buckets, E + 1 with the invalid one)
     const int64_t Tmax = M * A / 16 + (E + 1 < M * A ? E + 1 : M * A) + 1;
     SB_CHECK(Tmax <= 65535, fn, ": ", Tmax, " tile slots exceed the grid");
     const dim3 grid((unsigned)((w.N + 7) / 8), (unsigned)Tmax), block(256);
-    if (act == kF32) grouped_f32_kernel<float, false><<<grid, block, 0, st>>>((const float *)x, w, wsi, A, (float *)y, nullptr);
-    else grouped_f32_kernel<uint16_t, false><<<grid, block, 0, st>>>((const uint16_t *)x, w, wsi, A, (uint16_t *)y, nullptr);
+    if (act == kF32) grouped_f32_kernel<float, false><<<grid, block, 0, st>>>((const float *)x, w, wsi, A, (float *)y, nullptr, (int32_t)(M * A), (int32_t)E);
+    else grouped_f32_kernel<uint16_t, false><<<grid, block, 0, st>>>((const uint16_t *)x, w, wsi, A, (uint16_t *)y, nullptr, (int32_t)(M * A), (int32_t)E);
     SB_LAUNCH_OK(fn, " ", act_name(act), " M=", M, " A=", A, " E=", E, " N=", w.N, " K=", w.K, " G=", w.G);
     return 0;
 }
@@ -444,13 +447,13 @@ int combine_grouped(const char *fn, const void *h, const StackView &w, int64_t E
     auto st = static_cast<cudaStream_t>(stream);
     const auto *wsi = static_cast<const int32_t *>(ws);
     if (math != STRIX_MATH_F32) {
-        SB_TRY(grouped_umma(fn, h, w, wsi, M, A, nullptr, partial, act, /*combine=*/true, st));
+        SB_TRY(grouped_umma(fn, h, w, wsi, M, A, E, nullptr, partial, act, /*combine=*/true, st));
     } else {
         const int64_t Tmax = M * A / 16 + (E + 1 < M * A ? E + 1 : M * A) + 1;  // as in gather_grouped
         SB_CHECK(Tmax <= 65535, fn, ": ", Tmax, " tile slots exceed the grid");
         const dim3 grid((unsigned)((w.N + 7) / 8), (unsigned)Tmax), block(256);
-        if (act == kF32) grouped_f32_kernel<float, true><<<grid, block, 0, st>>>((const float *)h, w, wsi, A, nullptr, partial);
-        else grouped_f32_kernel<uint16_t, true><<<grid, block, 0, st>>>((const uint16_t *)h, w, wsi, A, nullptr, partial);
+        if (act == kF32) grouped_f32_kernel<float, true><<<grid, block, 0, st>>>((const float *)h, w, wsi, A, nullptr, partial, (int32_t)(M * A), (int32_t)E);
+        else grouped_f32_kernel<uint16_t, true><<<grid, block, 0, st>>>((const uint16_t *)h, w, wsi, A, nullptr, partial, (int32_t)(M * A), (int32_t)E);
         SB_LAUNCH_OK(fn, " ", act_name(act), " M=", M, " A=", A, " E=", E, " N=", w.N, " K=", w.K, " G=", w.G);
     }
     const unsigned blocks = (unsigned)((M * w.N + 255) / 256);
@@ -521,6 +524,11 @@ int group_routes_multi(const char *fn, const int32_t *ids, int64_t S, int64_t E,
 
 extern "C" {
 
+unsigned int strix_workspace_refusal_count(void) {
+    unsigned int v = 0;
+    cudaMemcpyFromSymbol(&v, g_ws_refusals, sizeof(v));
+    return v + sb::grouped_umma_ws_refusals() + sb::prefill_ws_refusals();
+}
 unsigned int strix_umma_abort_count(void) { return sb::grouped_umma_aborts() + sb::prefill_aborts(); }
 void strix_umma_wait_cycles(unsigned long long *out32, int reset) { sb::prefill_cycles(out32, reset != 0); }
 

@@ -37,6 +37,7 @@ constexpr int kStageBytesA = kTileM * kBK * 2, kStageBytesB = kTileN * kBK * 2;
 constexpr int kThreads = 160;
 
 __device__ unsigned int g_umma_aborts = 0;
+__device__ unsigned int g_ws_refusals = 0;
 
 struct Shared {
     uint64_t full[kStages], empty[kStages], acc_full;
@@ -45,24 +46,36 @@ struct Shared {
     int32_t slots[kTileN];
 };
 
-template <typename T, bool COMBINE>
+// DENSE: no grouping workspace - one weight matrix (bucket 0) against all A = M token rows; tile blockIdx.y holds rows
+// 128 * blockIdx.y .. of x, row m is "slot" m, outputs y[m, :] (COMBINE selects the FP32 output array).
+template <typename T, bool COMBINE, bool DENSE>
 __global__ void __launch_bounds__(kThreads, 2)
-    grouped_umma_kernel(const T *x, StackView w, const int32_t *ws, int64_t A, T *y, float *partial) {
+    grouped_umma_kernel(const T *x, StackView w, const int32_t *ws, int64_t A, T *y, float *partial, int32_t S_call, int32_t E_call) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
-    const int32_t S = ws[1], E = ws[2], n_wtiles = ws[3];
-    const int wt = blockIdx.y;
-    if (wt >= n_wtiles) return;
-    const RouteTables rt = route_tables(ws, S, E);
-    const int32_t bucket = rt.wtile_bucket[wt], st = rt.wtile_start[wt];
-    const int32_t b0 = rt.offsets[bucket], b1 = rt.offsets[bucket + 1];
-    if ((st - b0) % kTileN != 0) return;  // the 64-slot tile tables: every other tile of a bucket starts a 128-slot tile
-    const int rows = min(kTileN, b1 - st);
+    int32_t E = 1, bucket = 0, st = 0;
+    int rows = 0;
+    RouteTables rt{};
+    if constexpr (DENSE) {
+        st = (int32_t)blockIdx.y * kTileN;
+        rows = (int)min((int64_t)kTileN, A - st);
+    } else {
+        if (!ws_is_for(ws, S_call, E_call, &g_ws_refusals)) return;
+        const int32_t S = S_call, n_wtiles = ws[3];
+        E = E_call;
+        const int wt = blockIdx.y;
+        if (wt >= n_wtiles) return;
+        rt = route_tables(ws, S, E);
+        bucket = rt.wtile_bucket[wt], st = rt.wtile_start[wt];
+        const int32_t b0 = rt.offsets[bucket], b1 = rt.offsets[bucket + 1];
+        if ((st - b0) % kTileN != 0) return;  // the 64-slot tile tables: every other tile of a bucket starts a 128-slot tile
+        rows = min(kTileN, b1 - st);
+    }
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int64_t N = w.N, K = w.K;
     const int64_t n0 = (int64_t)blockIdx.x * kTileM;
     const int rows_w = (int)(N - n0 < kTileM ? N - n0 : kTileM);
 
-    if (bucket == E) {  // invalid ids: NaN outputs (the grouping raised err)
+    if (!DENSE && bucket == E) {  // invalid ids: NaN outputs (the grouping raised err)
         for (int i = tid; i < rows * rows_w; i += kThreads) {
             const int r = i / rows_w, c = i - r * rows_w;
             const int64_t slot = rt.slots[st + r];
@@ -74,14 +87,14 @@ __global__ void __launch_bounds__(kThreads, 2)
 
     // shared memory: [stages][A 16 KB | B 16 KB] on a 1024-byte boundary, then the control block
     uint8_t *tiles = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-    Shared &sh = *reinterpret_cast<Shared *>(smem_raw + kStages * (kStageBytesA + kStageBytesB));
+    Shared &sh = *reinterpret_cast<Shared *>(tiles + kStages * (kStageBytesA + kStageBytesB));
     if (tid == 0) {
         for (int s = 0; s < kStages; ++s) mbar_init(&sh.full[s], 128), mbar_init(&sh.empty[s], 1);
         mbar_init(&sh.acc_full, 1);
         sh.abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (tid < kTileN) sh.slots[tid] = tid < rows ? rt.slots[st + tid] : -1;
+    if (tid < kTileN) sh.slots[tid] = tid < rows ? (DENSE ? st + tid : rt.slots[st + tid]) : -1;
     if (warp == 4) {  // tensor memory: 128 FP32 accumulator columns
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sh.tmem_base)), "r"(128u) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -103,7 +116,7 @@ __global__ void __launch_bounds__(kThreads, 2)
         const uint8_t *qrow = w.rows(bucket, bits) + (n0 + (row_ok ? t : 0)) * row_bytes(bits, K);
         const uint16_t *srow = w.scale + wrow * gpr, *mrow = w.minv + wrow * gpr;
         const int32_t slot = sh.slots[t];
-        const T *xrow = slot >= 0 ? x + (COMBINE ? (int64_t)slot : (int64_t)slot / A) * K : nullptr;
+        const T *xrow = slot >= 0 ? x + ((COMBINE || DENSE) ? (int64_t)slot : (int64_t)slot / A) * K : nullptr;
         for (int kb = 0; kb < nkb; ++kb) {
             const int s = kb % kStages;
             const uint32_t ph = (uint32_t)(kb / kStages) & 1u;
@@ -192,38 +205,68 @@ __global__ void __launch_bounds__(kThreads, 2)
     }
 }
 
-}  // namespace
-
-namespace sb {
-
-int grouped_umma(const char *fn, const void *x, const StackView &w, const int32_t *ws, int64_t M, int64_t A, void *y, float *partial,
-                 int act, bool combine, cudaStream_t stream) {
-    SB_CHECK(w.K % kBK == 0, fn, " (tensor cores): K = ", w.K, ", expected a multiple of ", kBK);
-    const int64_t S = M * A;
-    const size_t smem = (size_t)kStages * (kStageBytesA + kStageBytesB) + sizeof(Shared) + 1024;
+constexpr size_t kSmem = (size_t)kStages * (kStageBytesA + kStageBytesB) + sizeof(Shared) + 1024;
+int prepare(const char *fn, size_t smem) {
     static thread_local int prepared_dev = -1;
     int dev = 0;
     SB_CUDA(cudaGetDevice(&dev), fn);
     if (prepared_dev != dev) {
-        SB_CUDA(cudaFuncSetAttribute(grouped_umma_kernel<float, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), fn);
-        SB_CUDA(cudaFuncSetAttribute(grouped_umma_kernel<float, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), fn);
-        SB_CUDA(cudaFuncSetAttribute(grouped_umma_kernel<uint16_t, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), fn);
-        SB_CUDA(cudaFuncSetAttribute(grouped_umma_kernel<uint16_t, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), fn);
+        SB_CUDA(cudaFuncSetAttribute(grouped_umma_kernel<float, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), fn);
+        SB_CUDA(cudaFuncSetAttribute(grouped_umma_kernel<float, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), fn);
+        SB_CUDA(cudaFuncSetAttribute(grouped_umma_kernel<uint16_t, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), fn);
+        SB_CUDA(cudaFuncSetAttribute(grouped_umma_kernel<uint16_t, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), fn);
+        SB_CUDA(cudaFuncSetAttribute(grouped_umma_kernel<float, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), fn);
+        SB_CUDA(cudaFuncSetAttribute(grouped_umma_kernel<uint16_t, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), fn);
+        SB_CUDA(cudaFuncSetAttribute(grouped_umma_kernel<uint16_t, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), fn);
         prepared_dev = dev;
     }
+    return 0;
+}
+}  // namespace
+
+namespace sb {
+
+// y[M, N] = x[M, K] * dequant(W)^T for one quantized matrix on the tensor cores (the dense twin of the grouped projection:
+// strixite kernels/linear_wmma.hpp:21-24). out_act == act, or BF16 x -> F32 y.
+int dense_umma(const char *fn, const void *x, const StackView &w, int64_t M, void *y, int act, int out_act, cudaStream_t stream) {
+    SB_CHECK(w.K % kBK == 0, fn, ": K = ", w.K, ", expected a multiple of ", kBK);
+    SB_CHECK(out_act == act || (act == kBF16 && out_act == kF32), fn, ": out_act ", act_name(out_act), " for ", act_name(act), " inputs (same, or BF16 -> F32)");
+    const int64_t tiles = (M + kTileN - 1) / kTileN;
+    SB_CHECK(M >= 1 && tiles <= 65535, fn, ": M = ", M);
+    SB_TRY(prepare(fn, kSmem));
+    const dim3 grid((unsigned)((w.N + kTileM - 1) / kTileM), (unsigned)tiles), block(kThreads);
+    if (act == kF32) grouped_umma_kernel<float, false, true><<<grid, block, kSmem, stream>>>((const float *)x, w, nullptr, M, (float *)y, nullptr, 0, 0);
+    else if (out_act == kF32) grouped_umma_kernel<uint16_t, true, true><<<grid, block, kSmem, stream>>>((const uint16_t *)x, w, nullptr, M, nullptr, (float *)y, 0, 0);
+    else grouped_umma_kernel<uint16_t, false, true><<<grid, block, kSmem, stream>>>((const uint16_t *)x, w, nullptr, M, (uint16_t *)y, nullptr, 0, 0);
+    SB_LAUNCH_OK(fn, " M=", M, " N=", w.N, " K=", w.K, " G=", w.G);
+    return 0;
+}
+
+int grouped_umma(const char *fn, const void *x, const StackView &w, const int32_t *ws, int64_t M, int64_t A, int64_t E, void *y, float *partial,
+                 int act, bool combine, cudaStream_t stream) {
+    SB_CHECK(w.K % kBK == 0, fn, " (tensor cores): K = ", w.K, ", expected a multiple of ", kBK);
+    const int64_t S = M * A;
+    const size_t smem = kSmem;
+    SB_TRY(prepare(fn, smem));
     // grid.y covers the 64-slot tile table's capacity (S / 64 + E + 2 with E <= 1023); CTAs past the live tiles return at once
     const int64_t wtmax = S / 64 + 1023 + 2;
     SB_CHECK(wtmax <= 65535, fn, " (tensor cores): ", wtmax, " tile slots exceed the grid");
     const dim3 grid((unsigned)((w.N + kTileM - 1) / kTileM), (unsigned)wtmax), block(kThreads);
     if (act == kF32) {
-        if (combine) grouped_umma_kernel<float, true><<<grid, block, smem, stream>>>((const float *)x, w, ws, A, nullptr, partial);
-        else grouped_umma_kernel<float, false><<<grid, block, smem, stream>>>((const float *)x, w, ws, A, (float *)y, nullptr);
+        if (combine) grouped_umma_kernel<float, true, false><<<grid, block, smem, stream>>>((const float *)x, w, ws, A, nullptr, partial, (int32_t)(M * A), (int32_t)E);
+        else grouped_umma_kernel<float, false, false><<<grid, block, smem, stream>>>((const float *)x, w, ws, A, (float *)y, nullptr, (int32_t)(M * A), (int32_t)E);
     } else {
-        if (combine) grouped_umma_kernel<uint16_t, true><<<grid, block, smem, stream>>>((const uint16_t *)x, w, ws, A, nullptr, partial);
-        else grouped_umma_kernel<uint16_t, false><<<grid, block, smem, stream>>>((const uint16_t *)x, w, ws, A, (uint16_t *)y, nullptr);
+        if (combine) grouped_umma_kernel<uint16_t, true, false><<<grid, block, smem, stream>>>((const uint16_t *)x, w, ws, A, nullptr, partial, (int32_t)(M * A), (int32_t)E);
+        else grouped_umma_kernel<uint16_t, false, false><<<grid, block, smem, stream>>>((const uint16_t *)x, w, ws, A, (uint16_t *)y, nullptr, (int32_t)(M * A), (int32_t)E);
     }
     SB_LAUNCH_OK(fn, " (tensor cores) M=", M, " A=", A, " N=", w.N, " K=", w.K, " G=", w.G);
     return 0;
+}
+
+unsigned int grouped_umma_ws_refusals() {
+    unsigned int v = 0;
+    cudaMemcpyFromSymbol(&v, g_ws_refusals, sizeof(v));
+    return v;
 }
 
 unsigned int grouped_umma_aborts() {

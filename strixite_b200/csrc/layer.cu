@@ -132,6 +132,15 @@ int linear_any(int bits, const void *x, const strix_qview *w, void *y, int64_t M
     }
 }
 
+int linear_wmma_any(int bits, const void *x, const strix_qview *w, void *y, int64_t M, int act, int out_act, void *stream) {
+    switch (bits) {
+        case 4: return strix_linear_q4_wmma(x, w, y, M, act, out_act, stream);
+        case 5: return strix_linear_q5_wmma(x, w, y, M, act, out_act, stream);
+        case 6: return strix_linear_q6_wmma(x, w, y, M, act, out_act, stream);
+        default: return strix_linear_q8_wmma(x, w, y, M, act, out_act, stream);
+    }
+}
+
 }  // namespace
 
 extern "C" {
@@ -331,9 +340,12 @@ int strix_moe_layer_forward(strix_moe_layer *L, const void *x, int64_t M, void *
     }
     // 4. The shared expert as dense projections, then y += sigmoid(gate) * s (or y += s when always on).
     if (d.shared_mode == STRIX_SHARED_SEPARATE) {
-        SB_TRY(linear_any(d.sh_gate_up_bits, x, &d.sh_gate_up, L->gu, M, act, act, stream));
+        // many tokens with a tensor-core math mode: the dense tensor-core projections (strixite runtime/qweight.hpp:63-72)
+        const bool sh_tc = d.math != STRIX_MATH_F32 && M >= L->tensor_min && d.d % 64 == 0 && d.I % 64 == 0;
+        auto lin = sh_tc ? linear_wmma_any : linear_any;
+        SB_TRY(lin(d.sh_gate_up_bits, x, &d.sh_gate_up, L->gu, M, act, act, stream));
         SB_TRY(strix_swiglu(L->gu, L->sh_h, M, d.I, act, stream));
-        SB_TRY(linear_any(d.sh_down_bits, L->sh_h, &d.sh_down, L->sh_y, M, act, act, stream));
+        SB_TRY(lin(d.sh_down_bits, L->sh_h, &d.sh_down, L->sh_y, M, act, act, stream));
         if (L->gated) SB_TRY(strix_moe_shared_add(y, L->sh_y, L->logits + E, R, M, d.d, (uint32_t)E, act, router_err, stream));
         else SB_TRY(strix_residual_add(y, L->sh_y, M * d.d, act, stream));
     }

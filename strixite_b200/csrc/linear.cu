@@ -5,6 +5,7 @@
 #include "common.cuh"
 #include "prefill_umma.cuh"
 
+#include "grouped.cuh"
 #include "strixite_b200.h"
 
 namespace {
@@ -197,6 +198,46 @@ int strix_linear_bf16w(const void *x, const uint16_t *w, void *y, int64_t M, int
 int strix_linear_f32w(const void *x, const float *w, void *y, int64_t M, int64_t N, int64_t K, int act, int out_act,
                       void *stream) {
     return linear_w<float>("linear_f32w", x, w, y, M, N, K, act, out_act, stream);
+}
+
+// ---- the same projections on the tensor cores (strixite kernels/linear_wmma.hpp:21-29) ---------------------------------
+static int linear_q_wmma(const char *fn, int bits, const void *x, const strix_qview *wp, void *y, int64_t M, int act, int out_act, void *stream) {
+    SB_CHECK(wp != nullptr, fn, ": null weight view");
+    const strix_qview &w = *wp;
+    SB_CHECK(x != nullptr && y != nullptr && w.q != nullptr && w.scale != nullptr && w.minv != nullptr, fn, ": null pointer (x=", x, ", y=", y, ", q=",
+             (const void *)w.q, ")");
+    SB_CHECK(group_ok(w.G), fn, ": group size ", w.G, " unsupported (32, 64 or 128)");
+    SB_CHECK(w.N >= 1 && w.N <= 0x7fffffff && w.K >= w.G && w.K <= (1 << 24) && w.K % w.G == 0 && w.K % 64 == 0, fn, ": [", w.N, ", ", w.K,
+             "]: K must be a multiple of the group size ", w.G, " and of 64 (strixite kernels/linear_wmma.hpp:7)");
+    SB_CHECK(bits != 5 || w.K % 128 == 0, fn, ": Q5 K = ", w.K, " is not a multiple of 128");
+    SB_CHECK(aligned16(w.q) && aligned16(x), fn, ": code array ", (const void *)w.q, " and x ", x, " must be 16-byte aligned");
+    SB_CHECK(act_ok(act), fn, ": unsupported activation dtype ", act);
+    SB_CHECK(out_act == act || (act == kBF16 && out_act == kF32), fn, ": output dtype ", act_name(out_act), " with input ", act_name(act),
+             " unsupported (same dtype, or BF16 -> F32)");
+    SB_CHECK(apart(y, M * w.N * act_size(out_act), x, M * w.K * act_size(act)), fn, ": output y overlaps input x");
+    const sb::StackView sv{w.q, w.scale, w.minv, nullptr, nullptr, bits, w.N, w.K, w.G};
+    return sb::dense_umma(fn, x, sv, M, y, act, out_act, static_cast<cudaStream_t>(stream));
+}
+int strix_linear_q4_wmma(const void *x, const strix_qview *w, void *y, int64_t M, int act, int out_act, void *stream) {
+    return linear_q_wmma("linear_q4_wmma", 4, x, w, y, M, act, out_act, stream);
+}
+int strix_linear_q5_wmma(const void *x, const strix_qview *w, void *y, int64_t M, int act, int out_act, void *stream) {
+    return linear_q_wmma("linear_q5_wmma", 5, x, w, y, M, act, out_act, stream);
+}
+int strix_linear_q6_wmma(const void *x, const strix_qview *w, void *y, int64_t M, int act, int out_act, void *stream) {
+    return linear_q_wmma("linear_q6_wmma", 6, x, w, y, M, act, out_act, stream);
+}
+int strix_linear_q8_wmma(const void *x, const strix_qview *w, void *y, int64_t M, int act, int out_act, void *stream) {
+    return linear_q_wmma("linear_q8_wmma", 8, x, w, y, M, act, out_act, stream);
+}
+int strix_linear_bf16w_wmma(const void *x, const uint16_t *w, void *y, int64_t M, int64_t N, int64_t K, int act, int out_act, void *stream) {
+    const char *fn = "linear_bf16w_wmma";
+    SB_CHECK(x != nullptr && w != nullptr && y != nullptr, fn, ": null pointer");
+    SB_CHECK(act == STRIX_ACT_BF16 && out_act == STRIX_ACT_F32, fn, ": BF16 tokens with FP32 outputs only (the router projection), got ",
+             act_name(act), " -> ", act_name(out_act));
+    SB_CHECK(N >= 1 && sb::dense_bf16_ok(x, w, M, N, K) && reinterpret_cast<uintptr_t>(y) % 4 == 0, fn, ": M = ", M, ", N = ", N, ", K = ", K,
+             ": needs K % 64 == 0 and 16-byte aligned x and W");
+    return sb::dense_bf16(fn, x, w, static_cast<float *>(y), M, N, K, nullptr, 0, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

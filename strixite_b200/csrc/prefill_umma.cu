@@ -45,6 +45,7 @@ using namespace sb;
 using namespace sb::umma;
 
 __device__ unsigned int g_prefill_aborts = 0;
+__device__ unsigned int g_ws_refusals = 0;
 // Cycles the roles of the FFN kernels spent in their waits, summed over CTAs since the last reset (diagnostics):
 // [mode * 16 + i], i = 0 kernel total, 1 producer raw_empty, 2 producer consumed, 3 mma acc_empty, 4 mma full, 5 unused,
 // 6 dequant raw_full, 7 dequant consumed, 8 dequant total, 9 epilogue acc_full, 10 epilogue total, 11 work items.
@@ -96,9 +97,12 @@ struct Ctl {
 
 // ---------------------------------------------------------------------------------------------------------------
 // tiles[0] = number of tiles, then (bucket, first sorted position, slots) per tile; buckets in ascending order.
-__global__ void __launch_bounds__(1024) tiles_kernel(const int32_t *ws, int32_t *tiles, int tile_slots) {
+__global__ void __launch_bounds__(1024) tiles_kernel(const int32_t *ws, int32_t *tiles, int tile_slots, int32_t S, int32_t E) {
     __shared__ int32_t scan[1024];
-    const int32_t S = ws[1], E = ws[2];
+    if (!ws_is_for(ws, S, E, &g_ws_refusals)) {  // no tiles: the projections that follow have no work and store nothing
+        if (threadIdx.x == 0) tiles[0] = 0;
+        return;
+    }
     const RouteTables rt = route_tables(ws, S, E);
     const int e = threadIdx.x;
     const int32_t cnt = e < E ? rt.offsets[e + 1] - rt.offsets[e] : 0;
@@ -121,8 +125,9 @@ __global__ void __launch_bounds__(1024) tiles_kernel(const int32_t *ws, int32_t 
 
 // One warp per sorted position p < offsets[E] (the slots with a valid expert).
 template <typename T>
-__global__ void __launch_bounds__(256) pregather_kernel(const T *x, const int32_t *row_index, const int32_t *ws, int64_t A, int64_t K, uint16_t *xg) {
-    const int32_t S = ws[1], E = ws[2];
+__global__ void __launch_bounds__(256) pregather_kernel(const T *x, const int32_t *row_index, const int32_t *ws, int64_t A, int64_t K, uint16_t *xg, int32_t S,
+                                                        int32_t E) {
+    if (ws[1] != S || ws[2] != E) return;  // counted by tiles_kernel
     const RouteTables rt = route_tables(ws, S, E);
     const int32_t total = rt.offsets[E];
     const int lane = threadIdx.x & 31;
@@ -650,12 +655,13 @@ int prefill_experts(PrefillPlan *p, const void *x, const int32_t *row_index, int
     const char *fn = "moe_layer_forward (tensor-core experts)";
     // a handful of tokens (decode, verify): tiles of 32 slots and four issuing warps; many tokens: tiles of 96 slots
     const bool small = M * A <= kSmallSlots;
-    tiles_kernel<<<1, 1024, 0, st>>>(ws, p->tiles, small ? FC<true>::TileSlots : FC<false>::TileSlots);
-    SB_LAUNCH_OK(fn, ": tiles");
     SB_CHECK(M * A <= p->max_tokens * p->A, fn, ": ", M * A, " slots exceed the layer's ", p->max_tokens * p->A);
+    const int32_t S = (int32_t)(M * A), E = (int32_t)p->Estack;
+    tiles_kernel<<<1, 1024, 0, st>>>(ws, p->tiles, small ? FC<true>::TileSlots : FC<false>::TileSlots, S, E);
+    SB_LAUNCH_OK(fn, ": tiles");
     const unsigned gblocks = (unsigned)std::min<int64_t>((M * A + 7) / 8, 148 * 16);
-    if (act == kF32) pregather_kernel<float><<<gblocks, 256, 0, st>>>((const float *)x, row_index, ws, A, p->d, p->xg);
-    else pregather_kernel<uint16_t><<<gblocks, 256, 0, st>>>((const uint16_t *)x, row_index, ws, A, p->d, p->xg);
+    if (act == kF32) pregather_kernel<float><<<gblocks, 256, 0, st>>>((const float *)x, row_index, ws, A, p->d, p->xg, S, E);
+    else pregather_kernel<uint16_t><<<gblocks, 256, 0, st>>>((const uint16_t *)x, row_index, ws, A, p->d, p->xg, S, E);
     SB_LAUNCH_OK(fn, ": gather");
     FfnArgs a{};
     a.ws = ws, a.tiles = p->tiles;
@@ -676,6 +682,12 @@ void prefill_cycles(unsigned long long *out, bool reset) {
         unsigned long long z[32] = {};
         cudaMemcpyToSymbol(g_prefill_cycles, z, sizeof(z));
     }
+}
+
+unsigned int prefill_ws_refusals() {
+    unsigned int v = 0;
+    cudaMemcpyFromSymbol(&v, g_ws_refusals, sizeof(v));
+    return v;
 }
 
 unsigned int prefill_aborts() {

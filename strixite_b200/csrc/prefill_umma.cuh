@@ -29,6 +29,8 @@ int dense_bf16(const char *fn, const void *x, const uint16_t *w, float *y, int64
                cudaStream_t st);
 // CTAs of these kernels that gave up on a bounded wait since the library was loaded.
 unsigned int prefill_aborts();
+// Forwards refused because the grouping workspace was built for other sizes than the call stated.
+unsigned int prefill_ws_refusals();
 // Wait-cycle counters of the FFN kernels' roles, 2 x 16 words (diagnostics; see prefill_umma.cu). Synchronizes.
 void prefill_cycles(unsigned long long *out, bool reset);
 

@@ -267,6 +267,19 @@ def linear_qw(x, w, y, M, act, out_act=None, stream=None):
     _linear_q(w.bits, x, w.w, y, M, act, out_act, stream)
 
 
+def linear_qw_wmma(x, w, y, M, act, out_act=None, stream=None):
+    """strixite runtime/qweight.hpp:63-72 linear_qw_wmma: the dense projection of a quantized matrix on the tensor cores."""
+    w = w.w if isinstance(w, QWeightView) else w
+    if w.bits not in (4, 5, 6, 8):
+        raise StrixError("linear_qw_wmma: weight has %d bits (not loaded?), expected 4, 5, 6 or 8" % w.bits)
+    call("strix_linear_q%d_wmma" % w.bits, _p(x), C.byref(w.view()), _p(y), M, int(act), int(act if out_act is None else out_act), _s(stream))
+
+
+def linear_bf16w_wmma(x, w, y, M, N, K, act, out_act=None, stream=None):
+    """strixite kernels/linear_wmma.hpp:27-29."""
+    call("strix_linear_bf16w_wmma", _p(x), _p(w), _p(y), M, N, K, int(act), int(act if out_act is None else out_act), _s(stream))
+
+
 def linear_bf16w(x, w, y, M, N, K, act, out_act=None, stream=None):
     """strixite kernels/linear.hpp:20-26. w: bfloat16 (or int16 bits) [N, K]."""
     call("strix_linear_bf16w", _p(x), _p(w), _p(y), M, N, K, int(act), int(act if out_act is None else out_act), _s(stream))
@@ -296,6 +309,30 @@ def hc_inject(x, y, w_in, M, N, H, act, stream=None):
 
 
 # ---- experts, per slot ---------------------------------------------------------------------------------------------
+
+
+def hc_mix_down(x, w, T, H, d, r, inject, eps, h, w_in, inv, act, stream=None):
+    """strixite kernels/hc.hpp:36-39: w a QWeight [r (+ H), H*d] in 4 or 8 bits (folded)."""
+    call("strix_hc_mix_down", _p(x), C.byref(w.view()), w.bits, T, H, d, r, int(bool(inject)), float(eps), _p(h), _p(w_in) if inject else None, _p(inv), int(act),
+         _s(stream))
+
+
+def hc_mix_up(h, w_up, x, norm_w, inv, T, H, d, u, act, stream=None):
+    """strixite kernels/hc.hpp:47-50: w_up a QWeight [H*d, r] whose arrays are chunk-major (to_chunk_major)."""
+    call("strix_hc_mix_up", _p(h), C.byref(w_up.view()), w_up.bits, _p(x), _p(norm_w), _p(inv), T, H, d, _p(u), int(act), _s(stream))
+
+
+def hc_inject_inv(x, w_in, y, T, H, d, eps, inv, act, stream=None):
+    """strixite kernels/hc_wmma.hpp:38-42: hc_inject and the updated streams' inverse RMS in one pass."""
+    call("strix_hc_inject_inv", _p(x), _p(w_in), _p(y), T, H, d, float(eps), _p(inv), int(act), _s(stream))
+
+
+def to_chunk_major(bits, q, scale, minv, N, K, G):
+    """strixite formats/q4.hpp:55 on host numpy arrays: (q, scale, minv) re-laid out chunk-major."""
+    qo, so, mo = np.empty_like(q), np.empty_like(scale), np.empty_like(minv)
+    call("strix_to_chunk_major", bits, q.ctypes.data_as(C.c_void_p), scale.ctypes.data_as(C.c_void_p), minv.ctypes.data_as(C.c_void_p), N, K, G,
+         qo.ctypes.data_as(C.c_void_p), so.ctypes.data_as(C.c_void_p), mo.ctypes.data_as(C.c_void_p))
+    return qo, so, mo
 
 
 def _experts(kind, bits, x, w, E, ids, coef, M, A, y, act, err, stream):
@@ -425,6 +462,11 @@ def moe_combine_reduce(partial, ids, coef, M, A, E, N, y, act, stream=None, pos=
 def umma_abort_count():
     """Thread blocks of the tensor-core kernels that abandoned a bounded wait since the library was loaded (0 when healthy)."""
     return int(lib.strix_umma_abort_count())
+
+
+def workspace_refusal_count():
+    """Launches that stored nothing because their grouping workspace was built for other sizes than the call stated."""
+    return int(lib.strix_workspace_refusal_count())
 
 
 def umma_wait_cycles(reset=True):

@@ -103,13 +103,11 @@ def test_one_rank_is_the_single_device_layer_bit_for_bit():
         assert layer.launches_per_step() > 0 and layer.received_slots() == T * (K_TOP + 1)
 
 
-@pytest.mark.parametrize("P,balanced", [(2, False), (4, True)])
-def test_several_ranks_emulated_on_one_gpu(P, balanced):
+def _emulate(P, balanced, L, x):
     """Every rank's backend lives on this GPU; the all-to-all is done by hand (block [s -> r] of rank s's send buffer becomes
     block s of rank r's receive buffer). The kernels, capacities and tables are exactly the multi-rank ones."""
     from strixite_b200 import ep as EP
 
-    L, x = _layer(), _tokens()
     Tl = T // P
     place = EP.placement(E, P, L["router_bias"], K_TOP, balanced=balanced)
     bes = [_backend(L, P, r, place, Tl) for r in range(P)]
@@ -129,6 +127,15 @@ def test_several_ranks_emulated_on_one_gpu(P, balanced):
     for r, be in enumerate(bes):
         back = torch.stack([summed[s][r] for s in range(P)])
         ys.append(to_np_act(be.home(0, back)))
+    return ys, bes
+
+
+@pytest.mark.parametrize("P,balanced", [(2, False), (4, True)])
+def test_several_ranks_emulated_on_one_gpu(P, balanced):
+    L, x = _layer(), _tokens()
+    Tl = T // P
+    ys, bes = _emulate(P, balanced, L, x)
+    for be in bes:
         be.check()
     y = np.concatenate(ys)
     want = _single_device(L, x[: Tl * P])
@@ -137,6 +144,26 @@ def test_several_ranks_emulated_on_one_gpu(P, balanced):
     assert (y != want).mean() < 0.02
     assert rel_err_rows(oracle.to_f32(y), oracle.to_f32(want)) < 2.0 ** -7
     assert sum(be.received_slots() for be in bes) == Tl * P * (K_TOP + 1)
+
+
+def test_a_token_with_a_non_finite_logit_poisons_only_itself():
+    """strixite kernels/moe_router.hpp: a token whose logits are not finite gets ids -1 and a NaN output row; every other
+    token of every rank is untouched, and the home rank's error word names it."""
+    from strixite_b200 import StrixError
+
+    L, x = _layer(), _tokens()
+    P, bad = 2, 5
+    clean, _ = _emulate(P, False, L, x)
+    xb = x.copy()
+    xb[bad] = oracle.f32_to_bf16(np.full(xb.shape[1], np.nan, np.float32)) if xb.dtype == np.uint16 else np.nan
+    ys, bes = _emulate(P, False, L, xb)
+    y, want = oracle.to_f32(np.concatenate(ys)), oracle.to_f32(np.concatenate(clean))
+    assert np.isnan(y[bad]).all()
+    keep = np.arange(y.shape[0]) != bad
+    assert np.array_equal(y[keep], want[keep])
+    with pytest.raises(StrixError):
+        bes[0].check()  # token 5 lives on rank 0
+    bes[1].check()
 
 
 def _run_rank(rank, world, port, out_dir, chunks):

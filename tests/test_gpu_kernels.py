@@ -102,6 +102,38 @@ def test_linear_q(act, bits, G, M):
 
 
 @pytest.mark.parametrize("act", ACTS)
+@pytest.mark.parametrize("bits,G", [(4, 128), (4, 32), (5, 128), (6, 64), (8, 64)])
+@pytest.mark.parametrize("M", (5, 130, 333))
+def test_linear_qw_wmma(act, bits, G, M):
+    # the dense projection on the tensor cores (strixite kernels/linear_wmma.hpp:21-24): F16 operands (one rounding of the
+    # dequantized weight and of an FP32 activation), FP32 accumulation - far inside the 2e-3 contract, not FP32-FMA exact
+    rng = np.random.default_rng(bits * 1000 + G + M)
+    N, Kd = 200, 512  # a ragged last tile of weight rows and of tokens
+    qw = quantized(rng, bits, N, Kd, G)
+    x = randn_act(rng, (M, Kd), act)
+    before = K.umma_abort_count()
+    for out_act in ({act, oracle.F32} if act == oracle.BF16 else {act}):
+        ref = oracle.linear_q(x, qw, out_act)
+        y = torch.empty((M, N), dtype=K._dtype(out_act), device="cuda")
+        K.linear_qw_wmma(to_torch_act(x), upload(qw), y, M, act, out_act)
+        assert rel_err_rows(oracle.to_f32(to_np_act(y)), oracle.to_f32(ref)) < 1e-3 + (BF16_ULP if out_act == oracle.BF16 else 0.0)
+    assert K.umma_abort_count() == before
+
+
+def test_linear_bf16w_wmma_matches_the_fma_kernel():
+    rng = np.random.default_rng(11)
+    M, N, Kd = 130, 513, 512
+    w = oracle.f32_to_bf16((rng.standard_normal((N, Kd)) * 0.02).astype(np.float32))
+    x = randn_act(rng, (M, Kd), oracle.BF16)
+    ref = oracle.linear_w(x, w, oracle.F32)
+    y = torch.empty((M, N), dtype=torch.float32, device="cuda")
+    K.linear_bf16w_wmma(to_torch_act(x), torch.from_numpy(w.view(np.int16)).cuda(), y, M, N, Kd, oracle.BF16, oracle.F32)
+    assert rel_err_rows(y.cpu().numpy(), ref) < 2e-5
+    with pytest.raises(StrixError, match="BF16 tokens with FP32 outputs"):
+        K.linear_bf16w_wmma(torch.zeros((M, Kd), device="cuda"), torch.from_numpy(w.view(np.int16)).cuda(), y, M, N, Kd, oracle.F32, oracle.F32)
+
+
+@pytest.mark.parametrize("act", ACTS)
 @pytest.mark.parametrize("wtype", ("f32", "bf16"))
 def test_linear_w(act, wtype):
     rng = np.random.default_rng(7)
@@ -307,6 +339,27 @@ def test_grouped_bad_id():
     K.linear_q4_experts_gather_grouped(to_torch_act(x), upload_stack(gu_st), E, ws, nbytes, M, A, y, K.Act.F32, K.MoeMath.F32)
     yy = y.cpu().numpy()
     assert host_err(err) == [1, 99, 15] and np.all(np.isnan(yy[7, 1])) and np.isnan(yy).sum() == 2 * I
+
+
+def test_grouped_refuses_a_workspace_grouped_for_other_sizes():
+    """A workspace built for (16 tokens, 4 slots, 16 experts) has the same byte size as one for (12, 4, 20), so the host's size
+    check passes - the kernels compare the header with the call's sizes, store nothing and count the refusal."""
+    rng = np.random.default_rng(23)
+    I, d = 64, 128
+    nbytes = K.moe_route_workspace_bytes(16, 4, 16)
+    assert nbytes == K.moe_route_workspace_bytes(12, 4, 20)
+    ids = np.stack([rng.permutation(16)[:4] for _ in range(16)]).astype(np.int32)
+    ws = torch.empty(nbytes // 4, dtype=torch.int32, device="cuda")
+    err = dev_err()
+    K.moe_group_routes(torch.from_numpy(ids).cuda(), 16, 4, 16, ws, nbytes, err)
+    w = upload_stack(make_stack(rng, 20, 2 * I, d, 32))
+    x = to_torch_act(randn_act(rng, (12, d), oracle.F32))
+    for math in (K.MoeMath.F32, K.MoeMath.WmmaF16):
+        before = K.workspace_refusal_count()
+        y = torch.full((12, 4, 2 * I), 7.0, device="cuda")
+        K.linear_q4_experts_gather_grouped(x, w, 20, ws, nbytes, 12, 4, y, K.Act.F32, math)
+        torch.cuda.synchronize()
+        assert bool((y == 7.0).all()) and K.workspace_refusal_count() == before + 1
 
 
 @pytest.mark.parametrize("act", ACTS)
