@@ -323,10 +323,12 @@ int64_t strix_ep_meta_ints(int64_t C, int64_t Cs);
 /* Home rank, after moe_router: ids / coef [T, A] (id E = the stacked shared expert, kept home; an invalid id stays home with
  * local id -1 and poisons the token), owner / local_of [E + 1] (rank and local index of every routed expert) ->
  * rowtok [P, C] (the token behind every row to send), meta [P, MW], pos [T, P] (row of token t in destination r's block, or
- * -1). flags[0] / flags[1] receive the largest row / slot count that exceeded C / Cs (0 = the step fitted). */
+ * -1). flags[0] / flags[1] receive the largest row / slot count that exceeded C / Cs (0 = the step fitted). scratch:
+ * strix_ep_plan_scratch_ints(T) int32 of device memory the call may overwrite (per-segment counts of its three launches). */
+int64_t strix_ep_plan_scratch_ints(int64_t T);
 int strix_ep_plan(const int32_t *ids, const float *coef, int64_t T, int64_t A, int64_t E, const int32_t *owner,
                   const int32_t *local_of, int P, int rank, int64_t C, int64_t Cs, int32_t *rowtok, int32_t *meta, int32_t *pos,
-                  uint32_t *flags, void *stream);
+                  uint32_t *flags, int32_t *scratch, void *stream);
 /* rows_send[r, i, :] = x[rowtok[r, i], :] for the rows the plan counted. */
 int strix_ep_gather_rows(const void *x, int64_t d, int act, const int32_t *rowtok, const int32_t *meta, int P, int64_t C,
                          int64_t Cs, void *rows_send, void *stream);

@@ -93,7 +93,8 @@ SIGNATURES = {
     "strix_linear_qmix_experts_combine_grouped": [_vp, _qm, _vp, _vp, _vp, _sz, _vp, _i64, _i64, _vp, _int, _int, _vp],
     "strix_moe_combine_reduce": [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _int, _vp],
     "strix_ep_meta_ints": [_i64, _i64],
-    "strix_ep_plan": [_vp, _vp, _i64, _i64, _i64, _vp, _vp, _int, _int, _i64, _i64, _vp, _vp, _vp, _vp, _vp],
+    "strix_ep_plan_scratch_ints": [_i64],
+    "strix_ep_plan": [_vp, _vp, _i64, _i64, _i64, _vp, _vp, _int, _int, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp],
     "strix_ep_gather_rows": [_vp, _i64, _int, _vp, _vp, _int, _i64, _i64, _vp, _vp],
     "strix_ep_unpack": [_vp, _int, _i64, _i64, _vp, _vp, _vp],
     "strix_ep_row_sum": [_vp, _vp, _int, _i64, _i64, _i64, _vp, _vp],
@@ -108,6 +109,7 @@ SIGNATURES = {
 _RESTYPES = {
     "strix_row_bytes": _i64,
     "strix_ep_meta_ints": _i64,
+    "strix_ep_plan_scratch_ints": _i64,
     "strix_hash64": C.c_uint64,
     "strix_umma_abort_count": C.c_uint,
     "strix_workspace_refusal_count": C.c_uint,

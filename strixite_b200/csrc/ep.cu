@@ -18,34 +18,7 @@ namespace {
 using namespace sb;
 
 constexpr int kMaxRanks = 8;
-constexpr int kPlanThreads = 1024;
-
-// Exclusive scan of one int per thread over the block; *total receives the sum. warp_tot: 32 ints of shared memory.
-__device__ int plan_scan(int v, int *warp_tot, int *total) {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    int incl = v;
-#pragma unroll
-    for (int off = 1; off < 32; off <<= 1) {
-        const int o = __shfl_up_sync(0xffffffffu, incl, off);
-        if (lane >= off) incl += o;
-    }
-    if (lane == 31) warp_tot[warp] = incl;
-    __syncthreads();
-    if (warp == 0) {
-        int t = warp_tot[lane], ti = t;
-#pragma unroll
-        for (int off = 1; off < 32; off <<= 1) {
-            const int o = __shfl_up_sync(0xffffffffu, ti, off);
-            if (lane >= off) ti += o;
-        }
-        warp_tot[lane] = ti - t;
-        if (lane == 31) *total = ti;
-    }
-    __syncthreads();
-    const int res = warp_tot[warp] + incl - v;
-    __syncthreads();
-    return res;
-}
+constexpr int kPlanThreads = 256;  // tokens per block of the plan kernels: a thread per token
 
 // The destination of slot id: its owner; the stacked shared expert (id == E) and invalid ids stay on the home rank (an
 // invalid id keeps local id -1 there, which poisons the token like on one device).
@@ -54,76 +27,123 @@ __device__ __forceinline__ void slot_dest(int32_t id, int E, const int32_t *owne
     else r = rank, loc = -1;
 }
 
-// One block. Thread i owns the contiguous tokens [i * tpt, (i + 1) * tpt): pass 1 counts its rows and slots per destination,
-// block scans turn the counts into first positions, pass 2 writes. Everything lands in token order.
+// A token's slots per destination: cnt[r] (0 = the token sends no row there).
+__device__ __forceinline__ void token_counts(const int32_t *ids, int t, int A, int E, const int32_t *owner, const int32_t *local_of, int rank, int (&cnt)[kMaxRanks]) {
+#pragma unroll
+    for (int q = 0; q < kMaxRanks; ++q) cnt[q] = 0;
+    for (int a = 0; a < A; ++a) {
+        int r, loc;
+        slot_dest(ids[(int64_t)t * A + a], E, owner, local_of, rank, r, loc);
+#pragma unroll
+        for (int q = 0; q < kMaxRanks; ++q) cnt[q] += q == r;
+    }
+}
+
+// The plan in three launches, deterministic and in token order per destination:
+//   count  block b = tokens [256 b, 256 b + 256): seg[b][r] = {rows, slots} the segment sends to destination r
+//   scan   one block, a warp per destination: seg[b][r] becomes the segment's first row / first slot; message headers, overflow flags
+//   place  block b again: a block-wide exclusive scan over its tokens gives each token its row and first slot; it writes them
 __global__ void __launch_bounds__(kPlanThreads)
-    ep_plan_kernel(const int32_t *ids, const float *coef, int T, int A, int E, const int32_t *owner, const int32_t *local_of, int P, int rank, int C,
-                   int Cs, int32_t *rowtok, int32_t *meta, int32_t *pos, uint32_t *flags) {
-    __shared__ int warp_tot[32];
-    __shared__ int tot_rows[kMaxRanks], tot_slots[kMaxRanks];
-    const int t0 = threadIdx.x, MW = 4 + 2 * C + 3 * Cs;
-    const int tpt = (T + kPlanThreads - 1) / kPlanThreads;
-    const int tb = min(T, t0 * tpt), te = min(T, tb + tpt);
-    int rows[kMaxRanks], slots[kMaxRanks];
+    ep_plan_count_kernel(const int32_t *ids, int T, int A, int E, const int32_t *owner, const int32_t *local_of, int P, int rank, int32_t *seg) {
+    __shared__ int wrows[kPlanThreads / 32][kMaxRanks], wslots[kPlanThreads / 32][kMaxRanks];
+    const int t = blockIdx.x * kPlanThreads + threadIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int cnt[kMaxRanks];
+    if (t < T) token_counts(ids, t, A, E, owner, local_of, rank, cnt);
+    else
 #pragma unroll
-    for (int r = 0; r < kMaxRanks; ++r) rows[r] = 0, slots[r] = 0;
-    for (int t = tb; t < te; ++t) {
-        unsigned seen = 0;
-        for (int a = 0; a < A; ++a) {
-            int r, loc;
-            slot_dest(ids[t * A + a], E, owner, local_of, rank, r, loc);
+        for (int q = 0; q < kMaxRanks; ++q) cnt[q] = 0;
 #pragma unroll
-            for (int q = 0; q < kMaxRanks; ++q)
-                if (q == r) slots[q] += 1, rows[q] += !(seen >> q & 1u);
-            seen |= 1u << r;
+    for (int q = 0; q < kMaxRanks; ++q) {
+        const int rows = __popc(__ballot_sync(0xffffffffu, cnt[q] > 0)), slots = __reduce_add_sync(0xffffffffu, cnt[q]);
+        if (lane == 0) wrows[warp][q] = rows, wslots[warp][q] = slots;
+    }
+    __syncthreads();
+    if (threadIdx.x < kMaxRanks) {
+        int rows = 0, slots = 0;
+        for (int w = 0; w < kPlanThreads / 32; ++w) rows += wrows[w][threadIdx.x], slots += wslots[w][threadIdx.x];
+        seg[((int64_t)blockIdx.x * kMaxRanks + threadIdx.x) * 2] = rows;
+        seg[((int64_t)blockIdx.x * kMaxRanks + threadIdx.x) * 2 + 1] = slots;
+    }
+}
+
+__global__ void __launch_bounds__(32 * kMaxRanks) ep_plan_scan_kernel(int32_t *seg, int nseg, int P, int C, int Cs, int32_t *meta, uint32_t *flags) {
+    const int r = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (r >= P) return;
+    int row_base = 0, slot_base = 0;
+    for (int b0 = 0; b0 < nseg; b0 += 32) {
+        const int b = b0 + lane;
+        int32_t *e = seg + ((int64_t)b * kMaxRanks + r) * 2;
+        const int rows = b < nseg ? e[0] : 0, slots = b < nseg ? e[1] : 0;
+        int ri = rows, si = slots;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+            const int o = __shfl_up_sync(0xffffffffu, ri, off), o2 = __shfl_up_sync(0xffffffffu, si, off);
+            if (lane >= off) ri += o, si += o2;
+        }
+        if (b < nseg) e[0] = row_base + ri - rows, e[1] = slot_base + si - slots;
+        row_base += __shfl_sync(0xffffffffu, ri, 31), slot_base += __shfl_sync(0xffffffffu, si, 31);
+    }
+    if (lane == 0) {
+        if (row_base > C) atomicMax(&flags[0], (uint32_t)row_base);
+        if (slot_base > Cs) atomicMax(&flags[1], (uint32_t)slot_base);
+        int32_t *m = meta + (int64_t)r * (4 + 2 * C + 3 * Cs);
+        m[0] = min(row_base, C), m[1] = min(slot_base, Cs), m[2] = 0, m[3] = 0;
+    }
+}
+
+__global__ void __launch_bounds__(kPlanThreads)
+    ep_plan_place_kernel(const int32_t *ids, const float *coef, int T, int A, int E, const int32_t *owner, const int32_t *local_of, int P, int rank, int C, int Cs,
+                         const int32_t *seg, int32_t *rowtok, int32_t *meta, int32_t *pos) {
+    __shared__ int wrows[kPlanThreads / 32][kMaxRanks], wslots[kPlanThreads / 32][kMaxRanks];
+    const int t = blockIdx.x * kPlanThreads + threadIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, MW = 4 + 2 * C + 3 * Cs;
+    int cnt[kMaxRanks], row[kMaxRanks], slot[kMaxRanks];
+    if (t < T) token_counts(ids, t, A, E, owner, local_of, rank, cnt);
+    else
+#pragma unroll
+        for (int q = 0; q < kMaxRanks; ++q) cnt[q] = 0;
+    // exclusive prefix inside the warp, then the warps before this one
+#pragma unroll
+    for (int q = 0; q < kMaxRanks; ++q) {
+        const unsigned has = __ballot_sync(0xffffffffu, cnt[q] > 0);
+        int si = cnt[q];
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+            const int o = __shfl_up_sync(0xffffffffu, si, off);
+            if (lane >= off) si += o;
+        }
+        row[q] = __popc(has & ((1u << lane) - 1u)), slot[q] = si - cnt[q];
+        if (lane == 31) wrows[warp][q] = __popc(has), wslots[warp][q] = si;
+    }
+    __syncthreads();
+    if (t >= T) return;
+#pragma unroll
+    for (int q = 0; q < kMaxRanks; ++q) {
+        if (q >= P) continue;
+        int rb = seg[((int64_t)blockIdx.x * kMaxRanks + q) * 2], sb_ = seg[((int64_t)blockIdx.x * kMaxRanks + q) * 2 + 1];
+        for (int w = 0; w < warp; ++w) rb += wrows[w][q], sb_ += wslots[w][q];
+        row[q] += rb, slot[q] += sb_;
+        const bool sends = cnt[q] > 0 && row[q] < C;
+        pos[(int64_t)t * P + q] = sends ? row[q] : -1;
+        if (sends) {
+            int32_t *m = meta + (int64_t)q * MW;
+            rowtok[(int64_t)q * C + row[q]] = t;
+            m[4 + 2 * row[q]] = slot[q];
+            m[4 + 2 * row[q] + 1] = max(0, min(cnt[q], Cs - slot[q]));  // slots past the capacity are dropped (the overflow flag is up)
         }
     }
-    int row0[kMaxRanks], slot0[kMaxRanks];
+    // the slots, in slot order per destination
+    for (int a = 0; a < A; ++a) {
+        int r, loc;
+        slot_dest(ids[(int64_t)t * A + a], E, owner, local_of, rank, r, loc);
 #pragma unroll
-    for (int r = 0; r < kMaxRanks; ++r) {
-        row0[r] = 0, slot0[r] = 0;
-        if (r < P) {
-            row0[r] = plan_scan(rows[r], warp_tot, &tot_rows[r]);
-            slot0[r] = plan_scan(slots[r], warp_tot, &tot_slots[r]);
-        }
-    }
-    if (t0 < P) {
-        const int nr = tot_rows[t0], ns = tot_slots[t0];
-        if (nr > C) atomicMax(&flags[0], (uint32_t)nr);
-        if (ns > Cs) atomicMax(&flags[1], (uint32_t)ns);
-        int32_t *m = meta + (int64_t)t0 * MW;
-        m[0] = min(nr, C), m[1] = min(ns, Cs), m[2] = 0, m[3] = 0;
-    }
-    for (int t = tb; t < te; ++t) {
-        // a token's slots per destination, in slot order; the row is opened by its first slot there
-        int row_of[kMaxRanks];
-#pragma unroll
-        for (int r = 0; r < kMaxRanks; ++r) row_of[r] = -1;
-        for (int a = 0; a < A; ++a) {
-            int r, loc;
-            slot_dest(ids[t * A + a], E, owner, local_of, rank, r, loc);
-#pragma unroll
-            for (int q = 0; q < kMaxRanks; ++q) {
-                if (q != r) continue;
-                int32_t *m = meta + (int64_t)q * MW;
-                if (row_of[q] < 0) {
-                    row_of[q] = row0[q]++;
-                    if (row_of[q] < C) {
-                        rowtok[(int64_t)q * C + row_of[q]] = t;
-                        m[4 + 2 * row_of[q]] = slot0[q], m[4 + 2 * row_of[q] + 1] = 0;
-                    }
-                }
-                const int j = slot0[q]++;
-                if (j < Cs && row_of[q] < C) {
-                    int32_t *sm = m + 4 + 2 * C + 3 * j;
-                    sm[0] = loc, sm[1] = row_of[q], sm[2] = __float_as_int(coef[t * A + a]);
-                    m[4 + 2 * row_of[q] + 1] += 1;  // this thread owns the row
-                }
+        for (int q = 0; q < kMaxRanks; ++q) {
+            if (q != r) continue;
+            const int j = slot[q]++;
+            if (j < Cs && row[q] < C) {
+                int32_t *sm = meta + (int64_t)q * MW + 4 + 2 * C + 3 * j;
+                sm[0] = loc, sm[1] = row[q], sm[2] = __float_as_int(coef[(int64_t)t * A + a]);
             }
         }
-#pragma unroll
-        for (int r = 0; r < kMaxRanks; ++r)
-            if (r < P) pos[(int64_t)t * P + r] = row_of[r] < C ? row_of[r] : -1;
     }
 }
 
@@ -200,15 +220,20 @@ extern "C" {
 
 int64_t strix_ep_meta_ints(int64_t C, int64_t Cs) { return 4 + 2 * C + 3 * Cs; }
 
+int64_t strix_ep_plan_scratch_ints(int64_t T) { return (T + kPlanThreads - 1) / kPlanThreads * kMaxRanks * 2; }
+
 int strix_ep_plan(const int32_t *ids, const float *coef, int64_t T, int64_t A, int64_t E, const int32_t *owner, const int32_t *local_of, int P, int rank,
-                  int64_t C, int64_t Cs, int32_t *rowtok, int32_t *meta, int32_t *pos, uint32_t *flags, void *stream) {
+                  int64_t C, int64_t Cs, int32_t *rowtok, int32_t *meta, int32_t *pos, uint32_t *flags, int32_t *scratch, void *stream) {
     const char *fn = "ep_plan";
-    SB_CHECK(ids && coef && owner && local_of && rowtok && meta && pos && flags, fn, ": null pointer");
+    SB_CHECK(ids && coef && owner && local_of && rowtok && meta && pos && flags && scratch, fn, ": null pointer");
     SB_CHECK(P >= 1 && P <= kMaxRanks && rank >= 0 && rank < P, fn, ": ", P, " ranks (1..", kMaxRanks, "), rank ", rank);
     SB_CHECK(T >= 1 && A >= 1 && A <= 64 && E >= 1 && T * A <= (1 << 22) && C >= 1 && Cs >= 1 && C <= (1 << 22) && Cs <= (1 << 24), fn, ": T = ", T, ", A = ", A,
              ", E = ", E, ", C = ", C, ", Cs = ", Cs);
-    ep_plan_kernel<<<1, kPlanThreads, 0, static_cast<cudaStream_t>(stream)>>>(ids, coef, (int)T, (int)A, (int)E, owner, local_of, P, rank, (int)C, (int)Cs, rowtok, meta,
-                                                                              pos, flags);
+    auto st = static_cast<cudaStream_t>(stream);
+    const int nseg = (int)((T + kPlanThreads - 1) / kPlanThreads);
+    ep_plan_count_kernel<<<nseg, kPlanThreads, 0, st>>>(ids, (int)T, (int)A, (int)E, owner, local_of, P, rank, scratch);
+    ep_plan_scan_kernel<<<1, 32 * kMaxRanks, 0, st>>>(scratch, nseg, P, (int)C, (int)Cs, meta, flags);
+    ep_plan_place_kernel<<<nseg, kPlanThreads, 0, st>>>(ids, coef, (int)T, (int)A, (int)E, owner, local_of, P, rank, (int)C, (int)Cs, scratch, rowtok, meta, pos);
     SB_LAUNCH_OK(fn);
     return 0;
 }

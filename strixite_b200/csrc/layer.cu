@@ -11,6 +11,22 @@
 #include <cstring>
 #include <new>
 
+// Built with -DSTRIX_NVTX only: named host ranges around the phases a forward enqueues, for a timeline profiler.
+#ifdef STRIX_NVTX
+#include <nvtx3/nvToolsExt.h>
+namespace {
+struct NvtxRange {
+    explicit NvtxRange(const char *name) { nvtxRangePushA(name); }
+    ~NvtxRange() { nvtxRangePop(); }
+};
+}  // namespace
+#define STRIX_RANGE(var, name) NvtxRange var(name)
+#else
+#define STRIX_RANGE(var, name) \
+    do {                       \
+    } while (0)
+#endif
+
 namespace {
 
 using namespace sb;
@@ -281,9 +297,11 @@ int strix_moe_layer_forward(strix_moe_layer *L, const void *x, int64_t M, void *
         p.sh_gate_up_bits = d.sh_gate_up_bits, p.sh_down_bits = d.sh_down_bits, p.sh_gate_up = d.sh_gate_up, p.sh_down = d.sh_down;
         p.logits = L->logits, p.ids = L->ids, p.coef = L->coef, p.hh = L->hh, p.sh_h = L->sh_h, p.hrec = L->hrec, p.err = L->err, p.sync = L->sync;
         // the plan was made for min(max_tokens, 8) tokens; fewer tokens only leave more room
+        STRIX_RANGE(r_decode, "strix moe decode (one kernel)");
         SB_TRY(sb::decode_stream_launch(fn, p, st));
         return 0;
     }
+    STRIX_RANGE(r_layer, "strix moe layer forward");
     // 1. Router logits, FP32 [M, R]; row E (when gated) is the shared expert's gate.
     const bool tensor_path = L->prefill != nullptr && M >= L->tensor_min;
     const bool dense_router = tensor_path && sb::prefill_has_dense_router(L->prefill);
@@ -310,6 +328,7 @@ int strix_moe_layer_forward(strix_moe_layer *L, const void *x, int64_t M, void *
     }
     // 3. Routed experts: grouped from grouped_min_tokens on, per slot below.
     if (tensor_path) {
+        STRIX_RANGE(r_experts, "strix moe experts (tensor cores)");
         // many tokens on the tensor cores: bucket-ordered F16 activations, gate/up with SwiGLU in its epilogue, down into
         // FP32 partials, then the ordered reduction of the reference's combine
         SB_TRY(sb::group_routes_multi(fn, L->ids, M * A, L->Estack, static_cast<int32_t *>(L->group_ws), L->route_scratch, expert_err, false, st));
@@ -340,6 +359,7 @@ int strix_moe_layer_forward(strix_moe_layer *L, const void *x, int64_t M, void *
     }
     // 4. The shared expert as dense projections, then y += sigmoid(gate) * s (or y += s when always on).
     if (d.shared_mode == STRIX_SHARED_SEPARATE) {
+        STRIX_RANGE(r_shared, "strix moe shared expert");
         // many tokens with a tensor-core math mode: the dense tensor-core projections (strixite runtime/qweight.hpp:63-72)
         const bool sh_tc = d.math != STRIX_MATH_F32 && M >= L->tensor_min && d.d % 64 == 0 && d.I % 64 == 0;
         auto lin = sh_tc ? linear_wmma_any : linear_any;

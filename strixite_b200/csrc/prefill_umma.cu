@@ -46,17 +46,30 @@ using namespace sb::umma;
 
 __device__ unsigned int g_prefill_aborts = 0;
 __device__ unsigned int g_ws_refusals = 0;
-// Cycles the roles of the FFN kernels spent in their waits, summed over CTAs since the last reset (diagnostics):
-// [mode * 16 + i], i = 0 kernel total, 1 producer raw_empty, 2 producer consumed, 3 mma acc_empty, 4 mma full, 5 unused,
+// Built with -DSTRIX_PROFILE only: cycles the roles of the FFN kernels spent in their waits, summed over CTAs since the last
+// reset: [mode * 16 + i], i = 0 kernel total, 1 producer raw_empty, 2 producer consumed, 3 mma acc_empty, 4 mma full, 5 unused,
 // 6 dequant raw_full, 7 dequant consumed, 8 dequant total, 9 epilogue acc_full, 10 epilogue total, 11 work items.
+// The product build has no clock reads and no counters in its kernels (strix_umma_wait_cycles then reports zeros).
+#ifdef STRIX_PROFILE
 __device__ unsigned long long g_prefill_cycles[32];
-
 #define TIMED_WAIT(slot, expr)                 \
     do {                                       \
         const long long t0_ = clock64();       \
         ok = (expr);                           \
         waited[slot] += clock64() - t0_;       \
     } while (0)
+#define PROFILE_ADD(i, v) atomicAdd(&g_prefill_cycles[MODE * 16 + (i)], (unsigned long long)(v))
+#define PROFILE_CLOCK() clock64()
+#else
+#define TIMED_WAIT(slot, expr) \
+    do {                       \
+        ok = (expr);           \
+    } while (0)
+#define PROFILE_ADD(i, v) \
+    do {                  \
+    } while (0)
+#define PROFILE_CLOCK() 0ll
+#endif
 
 constexpr int kBK = 64;                 // K per stage: 64 F16 = one 128-byte swizzle row
 constexpr int kTile = kTileM * kBK * 2;  // 16 KB: 128 rows x 64 F16 (the dense projection's operand tiles)
@@ -67,19 +80,25 @@ constexpr int kAStageCols = 64;         // an A stage in tensor memory: 2 row ha
 constexpr int kDequantWarps = 16;
 constexpr int64_t kSmallSlots = 1024;    // forwards with at most this many routed slots use the small-tile kernels
 
-// Two shapes of the FFN kernel. WIDE (many tokens): tiles of up to 96 slots, two accumulators (the work item's two row
-// halves), one MMA-issuing warp each. SMALL (a handful of tokens: decode, verify): tiles of up to 32 slots, and each row
-// half's K block split between two accumulators and two issuing warps (an instruction occupies its issuing thread ~100
-// cycles whatever N is, so with N = 16 the issue rate is all that matters; the epilogue adds the two halves in a fixed
-// order), a deeper A ring in the tensor-memory columns the narrow accumulators leave free.
-template <bool SMALL>
+// Three shapes of the FFN kernel. WIDE (many tokens): tiles of up to 96 slots, two accumulators (the work item's two row
+// halves), one MMA-issuing warp each, accumulators double-buffered against the epilogue. SMALL (a handful of tokens: decode,
+// verify): tiles of up to 32 slots, and each row half's K block split between two accumulators and two issuing warps (an
+// instruction occupies its issuing thread ~100 cycles whatever N is, so with N = 16 the issue rate is all that matters; the
+// epilogue adds the two halves in a fixed order), a deeper A ring in the tensor-memory columns the narrow accumulators leave
+// free. XWIDE (hundreds of slots per expert): tiles of up to 192 slots - half the instructions, dequantized weight stages and
+// barrier rounds per slot; the two 192-column accumulators fill tensor memory, so they are single-buffered (the epilogue of a
+// work item runs before the next item's first MMA; the item's main loop is twice as long as WIDE's).
+constexpr int kWide = 0, kSmall = 1, kXWide = 2;
+template <int SHAPE>
 struct FC {
-    static constexpr int TileSlots = SMALL ? 32 : 96;          // routed slots per tile = MMA N at most
+    static constexpr bool SMALL = SHAPE == kSmall, XW = SHAPE == kXWide;
+    static constexpr int TileSlots = SMALL ? 32 : XW ? 192 : 96;  // routed slots per tile = MMA N at most
     static constexpr int BTile = TileSlots * kBK * 2;         // the token tile of one K block
-    static constexpr int BS = SMALL ? 8 : 6;                  // token-tile stages (= ready / consumed barriers)
+    static constexpr int BS = SMALL ? 8 : XW ? 5 : 6;         // token-tile stages (= ready / consumed barriers)
     static constexpr int KSplit = SMALL ? 2 : 1;              // accumulators (and issuing warps) per row half
     static constexpr int NAcc = 2 * KSplit;
-    static constexpr int AccCols = TileSlots, BufCols = NAcc * AccCols, AColBase = 2 * BufCols;
+    static constexpr int AccBufs = XW ? 1 : 2;                // accumulator sets: 2 = the epilogue overlaps the next item's MMAs
+    static constexpr int AccCols = TileSlots, BufCols = NAcc * AccCols, AColBase = AccBufs * BufCols;
     static constexpr int AS = SMALL ? 4 : 2;                  // A stages in tensor memory
     static constexpr int EpiWarps = SMALL ? 4 : 8;
     static constexpr int ProducerWarp = kDequantWarps + EpiWarps, MmaWarp = ProducerWarp + 1;  // NAcc issuing warps from MmaWarp on
@@ -88,9 +107,9 @@ struct FC {
     static_assert(AS <= BS, "an A stage is freed through the barrier of the K block that used it");
 };
 
-template <bool SMALL>
+template <int SHAPE>
 struct Ctl {
-    uint64_t raw_full[kRS], raw_empty[kRS], full[FC<SMALL>::BS], consumed[FC<SMALL>::BS], acc_full[2], acc_empty[2];
+    uint64_t raw_full[kRS], raw_empty[kRS], full[FC<SHAPE>::BS], consumed[FC<SHAPE>::BS], acc_full[2], acc_empty[2];
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -151,25 +170,26 @@ struct FfnArgs {
 };
 
 __device__ __forceinline__ float bf16_rn(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
-// SwiGLU of one output; a BF16 activation pipeline rounds gate, up, silu(gate) and the product (strixite kernels/swiglu.hpp:21).
+// SwiGLU of one output with the reference's own operations (expf and an IEEE divide, strixite kernels/swiglu.hip:22); a BF16
+// activation pipeline rounds gate, up, silu(gate) and the product (strixite kernels/swiglu.hpp:21).
 __device__ __forceinline__ float swiglu_rounded(float g, float u, bool bf16) {
     if (bf16) {
         g = bf16_rn(g), u = bf16_rn(u);
-        return bf16_rn(bf16_rn(__fdividef(g, 1.0f + __expf(-g))) * u);
+        return bf16_rn(bf16_rn(g / (1.0f + expf(-g))) * u);
     }
-    return __fdividef(g, 1.0f + __expf(-g)) * u;
+    return g / (1.0f + expf(-g)) * u;
 }
 
-template <int MODE, int G, bool SMALL>
-__global__ void __launch_bounds__(FC<SMALL>::Threads, 1)
+template <int MODE, int G, int SHAPE>
+__global__ void __launch_bounds__(FC<SHAPE>::Threads, 1)
     ffn_umma_kernel(const __grid_constant__ CUtensorMap raw_map, const __grid_constant__ CUtensorMap b_map, const FfnArgs a) {
-    using C = FC<SMALL>;
+    using C = FC<SHAPE>;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t *base = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     uint8_t *b_stages = base, *raws = b_stages + C::BS * C::BTile;
-    Ctl<SMALL> &ctl = *reinterpret_cast<Ctl<SMALL> *>(raws + kRS * kRawStage);
+    Ctl<SHAPE> &ctl = *reinterpret_cast<Ctl<SHAPE> *>(raws + kRS * kRawStage);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const long long t_kernel = clock64();
+    [[maybe_unused]] const long long t_kernel = PROFILE_CLOCK();
     if (tid == 0) {
         for (int i = 0; i < kRS; ++i) mbar_init(&ctl.raw_full[i], 1), mbar_init(&ctl.raw_empty[i], kDequantWarps);
         // full[kc % BS]: K block kc is ready = its token tile has landed (the producer's arrival + bytes) and the 8 dequantizer
@@ -201,7 +221,7 @@ __global__ void __launch_bounds__(FC<SMALL>::Threads, 1)
         if (lane == 0) {
             uint32_t rawc = 0, bc = 0;
             bool ok = true;
-            long long waited[2] = {0, 0};
+            [[maybe_unused]] long long waited[2] = {0, 0};
             for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
                 const int32_t *t = a.tiles + 1 + 3 * (w / a.RB);
                 const int rb = w % a.RB, bucket = t[0], start = t[1];
@@ -224,8 +244,8 @@ __global__ void __launch_bounds__(FC<SMALL>::Threads, 1)
                     ++bc;
                 }
             }
-            atomicAdd(&g_prefill_cycles[MODE * 16 + 1], (unsigned long long)waited[0]);
-            atomicAdd(&g_prefill_cycles[MODE * 16 + 2], (unsigned long long)waited[1]);
+            PROFILE_ADD(1, waited[0]);
+            PROFILE_ADD(2, waited[1]);
         }
     } else if (warp >= C::MmaWarp) {
         // ---- MMA issuers: one warp per accumulator = (row half, K part). A tcgen05.mma occupies its issuing thread ~100 cycles
@@ -234,13 +254,13 @@ __global__ void __launch_bounds__(FC<SMALL>::Threads, 1)
         constexpr int KSteps = (kBK / 16) / C::KSplit;  // 16-element K steps of a K block per issuer
         uint32_t kc = 0, it = 0;
         bool ok = true, peeked = false;
-        long long waited[3] = {0, 0, 0};
+        [[maybe_unused]] long long waited[3] = {0, 0, 0};
         for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x, ++it) {
             const int32_t *t = a.tiles + 1 + 3 * (w / a.RB);
             const int n_mma = (t[2] + 15) & ~15;
             const uint32_t idesc = umma_idesc(n_mma);
-            const uint32_t buf = it & 1u;
-            if (lane == 0) TIMED_WAIT(0, mbar_wait(&ctl.acc_empty[buf], ((it >> 1) & 1u) ^ 1u, abort_flag));
+            const uint32_t buf = it % C::AccBufs;
+            if (lane == 0) TIMED_WAIT(0, mbar_wait(&ctl.acc_empty[buf], ((it / C::AccBufs) & 1u) ^ 1u, abort_flag));
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) break;
             tc_fence_after();
@@ -268,7 +288,7 @@ __global__ void __launch_bounds__(FC<SMALL>::Threads, 1)
             __syncwarp();
         }
         if (lane == 0 && ai == 0)
-            for (int i = 0; i < 3; ++i) atomicAdd(&g_prefill_cycles[MODE * 16 + 3 + i], (unsigned long long)waited[i]);
+            for (int i = 0; i < 3; ++i) PROFILE_ADD(3 + i, waited[i]);
         tc_fence_before();
     } else if (warp < kDequantWarps) {
         // ---- dequantizers: thread = (K block half kbl, row half acc, row r): 64 codes of one row per raw stage ----
@@ -277,8 +297,8 @@ __global__ void __launch_bounds__(FC<SMALL>::Threads, 1)
         constexpr int NG = G >= 64 ? 1 : 64 / G;  // groups in a thread's 64 codes
         uint32_t rawc = 0;
         bool ok = true;
-        long long waited[2] = {0, 0};
-        const long long t_start = clock64();
+        [[maybe_unused]] long long waited[2] = {0, 0};
+        [[maybe_unused]] const long long t_start = PROFILE_CLOCK();
         for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
             const int32_t *t = a.tiles + 1 + 3 * (w / a.RB);
             const int64_t row = (int64_t)first_row(t[0], w % a.RB, acc) + r;
@@ -322,9 +342,9 @@ __global__ void __launch_bounds__(FC<SMALL>::Threads, 1)
             }
         }
         if (tid == 0) {
-            atomicAdd(&g_prefill_cycles[MODE * 16 + 6], (unsigned long long)waited[0]);
-            atomicAdd(&g_prefill_cycles[MODE * 16 + 7], (unsigned long long)waited[1]);
-            atomicAdd(&g_prefill_cycles[MODE * 16 + 8], (unsigned long long)(clock64() - t_start));
+            PROFILE_ADD(6, waited[0]);
+            PROFILE_ADD(7, waited[1]);
+            PROFILE_ADD(8, (PROFILE_CLOCK() - t_start));
         }
     } else {
         // ---- epilogue: lane quadrant q = warp % 4; with 8 warps the two of a quadrant take alternate 16-column chunks ----
@@ -333,13 +353,13 @@ __global__ void __launch_bounds__(FC<SMALL>::Threads, 1)
         const RouteTables rtab = route_tables(a.ws, a.ws[1], a.ws[2]);
         uint32_t it = 0;
         bool ok = true;
-        long long waited[1] = {0};
-        const long long t_start = clock64();
+        [[maybe_unused]] long long waited[1] = {0};
+        [[maybe_unused]] const long long t_start = PROFILE_CLOCK();
         for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x, ++it) {
             const int32_t *t = a.tiles + 1 + 3 * (w / a.RB);
             const int rb = w % a.RB, start = t[1], n_valid = t[2];
-            const uint32_t buf = it & 1u;
-            TIMED_WAIT(0, mbar_wait(&ctl.acc_full[buf], (it >> 1) & 1u, abort_flag));
+            const uint32_t buf = it % C::AccBufs;
+            TIMED_WAIT(0, mbar_wait(&ctl.acc_full[buf], (it / C::AccBufs) & 1u, abort_flag));
             if (!ok) break;
             tc_fence_after();
             const uint32_t tbase = tmem + ((uint32_t)(q * 32) << 16) + buf * C::BufCols;
@@ -386,13 +406,13 @@ __global__ void __launch_bounds__(FC<SMALL>::Threads, 1)
             if (lane == 0) mbar_arrive(&ctl.acc_empty[buf]);
         }
         if (tid == kDequantWarps * 32) {
-            atomicAdd(&g_prefill_cycles[MODE * 16 + 9], (unsigned long long)waited[0]);
-            atomicAdd(&g_prefill_cycles[MODE * 16 + 10], (unsigned long long)(clock64() - t_start));
-            atomicAdd(&g_prefill_cycles[MODE * 16 + 11], (unsigned long long)it);
+            PROFILE_ADD(9, waited[0]);
+            PROFILE_ADD(10, (PROFILE_CLOCK() - t_start));
+            PROFILE_ADD(11, it);
         }
     }
     __syncthreads();
-    if (tid == 0) atomicAdd(&g_prefill_cycles[MODE * 16], (unsigned long long)(clock64() - t_kernel));
+    if (tid == 0) PROFILE_ADD(0, (PROFILE_CLOCK() - t_kernel));
     if (tid == 0 && ctl.abort_flag) atomicAdd(&g_prefill_aborts, 1u);
     if (warp == C::MmaWarp) {
         tc_fence_after();
@@ -520,29 +540,29 @@ int make_map(const char *fn, CUtensorMap *m, CUtensorMapDataType dt, int es, con
     return 0;
 }
 
-template <bool SMALL>
+template <int SHAPE>
 constexpr size_t ffn_smem() {
-    return (size_t)FC<SMALL>::BS * FC<SMALL>::BTile + (size_t)kRS * kRawStage + sizeof(Ctl<SMALL>) + 1024;
+    return (size_t)FC<SHAPE>::BS * FC<SHAPE>::BTile + (size_t)kRS * kRawStage + sizeof(Ctl<SHAPE>) + 1024;
 }
 constexpr size_t kDenseSmem = (size_t)kDS * 2 * kTile + sizeof(DenseCtl) + 1024;
 
-template <int MODE, bool SMALL>
+template <int MODE, int SHAPE>
 int launch_ffn(const char *fn, int G, const CUtensorMap &raw, const CUtensorMap &b, const FfnArgs &a, int ctas, cudaStream_t st) {
     static thread_local int prepared = -1;  // one per (MODE, SMALL) and host thread
-    constexpr size_t smem = ffn_smem<SMALL>();
-    constexpr int threads = FC<SMALL>::Threads;
+    constexpr size_t smem = ffn_smem<SHAPE>();
+    constexpr int threads = FC<SHAPE>::Threads;
     int dev = 0;
     SB_CUDA(cudaGetDevice(&dev), fn);
     if (prepared != dev) {
-        SB_CUDA(cudaFuncSetAttribute(ffn_umma_kernel<MODE, 32, SMALL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), fn);
-        SB_CUDA(cudaFuncSetAttribute(ffn_umma_kernel<MODE, 64, SMALL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), fn);
-        SB_CUDA(cudaFuncSetAttribute(ffn_umma_kernel<MODE, 128, SMALL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), fn);
+        SB_CUDA(cudaFuncSetAttribute(ffn_umma_kernel<MODE, 32, SHAPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), fn);
+        SB_CUDA(cudaFuncSetAttribute(ffn_umma_kernel<MODE, 64, SHAPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), fn);
+        SB_CUDA(cudaFuncSetAttribute(ffn_umma_kernel<MODE, 128, SHAPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), fn);
         prepared = dev;
     }
-    if (G == 32) ffn_umma_kernel<MODE, 32, SMALL><<<ctas, threads, smem, st>>>(raw, b, a);
-    else if (G == 64) ffn_umma_kernel<MODE, 64, SMALL><<<ctas, threads, smem, st>>>(raw, b, a);
-    else ffn_umma_kernel<MODE, 128, SMALL><<<ctas, threads, smem, st>>>(raw, b, a);
-    SB_LAUNCH_OK(fn, " (tcgen05 FFN stage ", MODE, SMALL ? ", small tiles" : "", ") K=", a.K, " G=", G);
+    if (G == 32) ffn_umma_kernel<MODE, 32, SHAPE><<<ctas, threads, smem, st>>>(raw, b, a);
+    else if (G == 64) ffn_umma_kernel<MODE, 64, SHAPE><<<ctas, threads, smem, st>>>(raw, b, a);
+    else ffn_umma_kernel<MODE, 128, SHAPE><<<ctas, threads, smem, st>>>(raw, b, a);
+    SB_LAUNCH_OK(fn, " (tcgen05 FFN stage ", MODE, SHAPE == kSmall ? ", small tiles" : SHAPE == kXWide ? ", 192-slot tiles" : "", ") K=", a.K, " G=", G);
     return 0;
 }
 
@@ -551,7 +571,7 @@ int launch_ffn(const char *fn, int G, const CUtensorMap &raw, const CUtensorMap 
 namespace sb {
 
 struct PrefillPlan {
-    CUtensorMap gu_raw, dn_raw, xg_map, hs_map, xg_map_s, hs_map_s, rw_map;  // _s: boxes of 32 rows for the small-tile kernels
+    CUtensorMap gu_raw, dn_raw, xg_map, hs_map, xg_map_s, hs_map_s, xg_map_x, hs_map_x, rw_map;  // _s / _x: boxes of 32 / 192 rows (small / 192-slot tiles)
     bool dense_router = false;
     int64_t d, I, Estack, max_tokens, A, router_rows;
     int G_gu, G_dn;
@@ -582,13 +602,15 @@ int prefill_create(const strix_moe_layer_desc &d, int64_t A, int64_t Estack, int
     };
     alloc(reinterpret_cast<void **>(&p->xg), (size_t)S * d.d * 2);
     alloc(reinterpret_cast<void **>(&p->hs), (size_t)S * d.I * 2);
-    alloc(reinterpret_cast<void **>(&p->tiles), (size_t)(1 + 3 * (S / FC<true>::TileSlots + Estack + 2)) * 4);
+    alloc(reinterpret_cast<void **>(&p->tiles), (size_t)(1 + 3 * (S / FC<kSmall>::TileSlots + Estack + 2)) * 4);
     if (rc == 0) rc = make_map(fn, &p->gu_raw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, d.gate_up.q, Estack * 2 * d.I, d.d / 2, 64, CU_TENSOR_MAP_SWIZZLE_64B);
     if (rc == 0) rc = make_map(fn, &p->dn_raw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, d.down.q, Estack * d.d, d.I / 2, 64, CU_TENSOR_MAP_SWIZZLE_64B);
-    if (rc == 0) rc = make_map(fn, &p->xg_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, p->xg, S, d.d, kBK, CU_TENSOR_MAP_SWIZZLE_128B, FC<false>::TileSlots);
-    if (rc == 0) rc = make_map(fn, &p->hs_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, p->hs, S, d.I, kBK, CU_TENSOR_MAP_SWIZZLE_128B, FC<false>::TileSlots);
-    if (rc == 0) rc = make_map(fn, &p->xg_map_s, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, p->xg, S, d.d, kBK, CU_TENSOR_MAP_SWIZZLE_128B, FC<true>::TileSlots);
-    if (rc == 0) rc = make_map(fn, &p->hs_map_s, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, p->hs, S, d.I, kBK, CU_TENSOR_MAP_SWIZZLE_128B, FC<true>::TileSlots);
+    if (rc == 0) rc = make_map(fn, &p->xg_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, p->xg, S, d.d, kBK, CU_TENSOR_MAP_SWIZZLE_128B, FC<kWide>::TileSlots);
+    if (rc == 0) rc = make_map(fn, &p->hs_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, p->hs, S, d.I, kBK, CU_TENSOR_MAP_SWIZZLE_128B, FC<kWide>::TileSlots);
+    if (rc == 0) rc = make_map(fn, &p->xg_map_s, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, p->xg, S, d.d, kBK, CU_TENSOR_MAP_SWIZZLE_128B, FC<kSmall>::TileSlots);
+    if (rc == 0) rc = make_map(fn, &p->hs_map_s, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, p->hs, S, d.I, kBK, CU_TENSOR_MAP_SWIZZLE_128B, FC<kSmall>::TileSlots);
+    if (rc == 0) rc = make_map(fn, &p->xg_map_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, p->xg, S, d.d, kBK, CU_TENSOR_MAP_SWIZZLE_128B, FC<kXWide>::TileSlots);
+    if (rc == 0) rc = make_map(fn, &p->hs_map_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, p->hs, S, d.I, kBK, CU_TENSOR_MAP_SWIZZLE_128B, FC<kXWide>::TileSlots);
     p->dense_router = d.act == kBF16 && d.router_kind == STRIX_ROUTER_BF16 && d.d % kBK == 0;
     if (rc == 0 && p->dense_router)
         rc = make_map(fn, &p->rw_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, d.router_w, router_rows, d.d, kBK, CU_TENSOR_MAP_SWIZZLE_128B);
@@ -653,11 +675,12 @@ bool dense_bf16_ok(const void *x, const void *w, int64_t M, int64_t N, int64_t K
 int prefill_experts(PrefillPlan *p, const void *x, const int32_t *row_index, int act, const int32_t *ws, int64_t M, int64_t A, float *partial,
                     cudaStream_t st) {
     const char *fn = "moe_layer_forward (tensor-core experts)";
-    // a handful of tokens (decode, verify): tiles of 32 slots and four issuing warps; many tokens: tiles of 96 slots
-    const bool small = M * A <= kSmallSlots;
+    // a handful of tokens (decode, verify): tiles of 32 slots and four issuing warps; many tokens: tiles of 96 slots; an average
+    // of more than a 96-slot tile per expert: tiles of 192 slots
+    const int shape = M * A <= kSmallSlots ? kSmall : M * A > (int64_t)FC<kWide>::TileSlots * p->Estack ? kXWide : kWide;
     SB_CHECK(M * A <= p->max_tokens * p->A, fn, ": ", M * A, " slots exceed the layer's ", p->max_tokens * p->A);
     const int32_t S = (int32_t)(M * A), E = (int32_t)p->Estack;
-    tiles_kernel<<<1, 1024, 0, st>>>(ws, p->tiles, small ? FC<true>::TileSlots : FC<false>::TileSlots, S, E);
+    tiles_kernel<<<1, 1024, 0, st>>>(ws, p->tiles, shape == kSmall ? FC<kSmall>::TileSlots : shape == kXWide ? FC<kXWide>::TileSlots : FC<kWide>::TileSlots, S, E);
     SB_LAUNCH_OK(fn, ": tiles");
     const unsigned gblocks = (unsigned)std::min<int64_t>((M * A + 7) / 8, 148 * 16);
     if (act == kF32) pregather_kernel<float><<<gblocks, 256, 0, st>>>((const float *)x, row_index, ws, A, p->d, p->xg, S, E);
@@ -667,21 +690,28 @@ int prefill_experts(PrefillPlan *p, const void *x, const int32_t *row_index, int
     a.ws = ws, a.tiles = p->tiles;
     a.scale = p->gu_scale, a.minv = p->gu_min, a.K = (int)p->d, a.rows_per_expert = (int)(2 * p->I), a.I = (int)p->I, a.RB = (int)(p->I / kTileM);
     a.hs = p->hs, a.partial = nullptr, a.N = 0, a.bf16_act = act == kBF16;
-    if (small) SB_TRY((launch_ffn<0, true>(fn, p->G_gu, p->gu_raw, p->xg_map_s, a, p->sms, st)));
-    else SB_TRY((launch_ffn<0, false>(fn, p->G_gu, p->gu_raw, p->xg_map, a, p->sms, st)));
+    if (shape == kSmall) SB_TRY((launch_ffn<0, kSmall>(fn, p->G_gu, p->gu_raw, p->xg_map_s, a, p->sms, st)));
+    else if (shape == kXWide) SB_TRY((launch_ffn<0, kXWide>(fn, p->G_gu, p->gu_raw, p->xg_map_x, a, p->sms, st)));
+    else SB_TRY((launch_ffn<0, kWide>(fn, p->G_gu, p->gu_raw, p->xg_map, a, p->sms, st)));
     a.scale = p->dn_scale, a.minv = p->dn_min, a.K = (int)p->I, a.rows_per_expert = (int)p->d, a.RB = (int)(p->d / (2 * kTileM));
     a.hs = nullptr, a.partial = partial, a.N = (int)p->d;
-    if (small) SB_TRY((launch_ffn<1, true>(fn, p->G_dn, p->dn_raw, p->hs_map_s, a, p->sms, st)));
-    else SB_TRY((launch_ffn<1, false>(fn, p->G_dn, p->dn_raw, p->hs_map, a, p->sms, st)));
+    if (shape == kSmall) SB_TRY((launch_ffn<1, kSmall>(fn, p->G_dn, p->dn_raw, p->hs_map_s, a, p->sms, st)));
+    else if (shape == kXWide) SB_TRY((launch_ffn<1, kXWide>(fn, p->G_dn, p->dn_raw, p->hs_map_x, a, p->sms, st)));
+    else SB_TRY((launch_ffn<1, kWide>(fn, p->G_dn, p->dn_raw, p->hs_map, a, p->sms, st)));
     return 0;
 }
 
 void prefill_cycles(unsigned long long *out, bool reset) {
+#ifdef STRIX_PROFILE
     cudaMemcpyFromSymbol(out, g_prefill_cycles, sizeof(unsigned long long) * 32);
     if (reset) {
         unsigned long long z[32] = {};
         cudaMemcpyToSymbol(g_prefill_cycles, z, sizeof(z));
     }
+#else
+    (void)reset;
+    for (int i = 0; i < 32; ++i) out[i] = 0;
+#endif
 }
 
 unsigned int prefill_ws_refusals() {

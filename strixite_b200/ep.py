@@ -200,6 +200,7 @@ class CudaBackend:
             self.c.append(dict(
                 shard=shard, logits=z(Tc, E + 1, dt=torch.float32), ids=z(Tc, self.A), coef=z(Tc, self.A, dt=torch.float32), err=K.new_err(dev),
                 rowtok=z(world, self.Cr), meta_send=z(world, self.MW), meta_recv=z(world, self.MW), pos=z(Tc, world), flags=z(2),
+                plan_scratch=z(int(lib.strix_ep_plan_scratch_ints(Tc))),
                 rows_send=z(world, self.Cr, d, dt=adt), rows_recv=z(world, self.Cr, d, dt=adt), slot_ids=z(n_cap), slot_row=z(n_cap),
                 partial=torch.empty((n_cap, d), dtype=torch.float32, device=dev), summed=z(world, self.Cr, d, dt=torch.float32),
                 back=z(world, self.Cr, d, dt=torch.float32), y=torch.empty((Tc, d), dtype=adt, device=dev)))
@@ -254,10 +255,10 @@ class CudaBackend:
         K, b = self.K, self.c[c]
         T = b["x"].shape[0]
         call("strix_ep_plan", K._p(b["ids"]), K._p(b["coef"]), T, self.A, self.E, K._p(self.owner), K._p(self.local_of), self.P, self.rank, self.Cr, self.Cs,
-             K._p(b["rowtok"]), K._p(b["meta_send"]), K._p(b["pos"]), K._p(b["flags"]), self._sp(c))
+             K._p(b["rowtok"]), K._p(b["meta_send"]), K._p(b["pos"]), K._p(b["flags"]), K._p(b["plan_scratch"]), self._sp(c))
         call("strix_ep_gather_rows", K._p(b["x"]), self.d, int(self.act), K._p(b["rowtok"]), K._p(b["meta_send"]), self.P, self.Cr, self.Cs, K._p(b["rows_send"]),
              self._sp(c))
-        self.launches += 2
+        self.launches += 4  # the plan is three launches (count, scan, place)
         return b["rows_send"], b["meta_send"]
 
     def experts(self, c, rows_recv, meta_recv):

@@ -48,7 +48,7 @@ def _backend(L, world, rank, place, Tl, chunks=1, device="cuda"):
 def test_plan_kernel_matches_its_numpy_restatement(P, rank):
     from strixite_b200 import ep as EP
     from strixite_b200 import kernels as K
-    from strixite_b200._lib import call
+    from strixite_b200._lib import call, lib
 
     rng = np.random.default_rng(P)
     Tn, A, En = 333, 5, 32
@@ -65,8 +65,9 @@ def test_plan_kernel_matches_its_numpy_restatement(P, rank):
         meta = torch.zeros((P, EP.meta_ints(Cr, Cs)), dtype=torch.int32, device="cuda")
         pos = torch.zeros((Tn, P), dtype=torch.int32, device="cuda")
         flags = torch.zeros(2, dtype=torch.int32, device="cuda")
+        scratch = torch.empty(int(lib.strix_ep_plan_scratch_ints(Tn)), dtype=torch.int32, device="cuda")
         call("strix_ep_plan", K._p(d_ids), K._p(d_coef), Tn, A, En, K._p(d_owner), K._p(d_local), P, rank, Cr, Cs,
-             K._p(rowtok), K._p(meta), K._p(pos), K._p(flags), K._s(None))
+             K._p(rowtok), K._p(meta), K._p(pos), K._p(flags), K._p(scratch), K._s(None))
         assert np.array_equal(flags.cpu().numpy().view(np.uint32), want[3])
         m, wm = meta.cpu().numpy(), want[1]
         assert np.array_equal(m[:, :2], wm[:, :2])

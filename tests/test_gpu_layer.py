@@ -6,14 +6,14 @@ import pytest
 import torch
 
 import oracle
-from helpers import BF16_ULP, bf16_rows_close, gpu_layer, make_layer, randn_act, rel_err_rows, to_np_act, to_torch_act
+from helpers import gpu_layer, make_layer, randn_act, rel_err_rows, to_np_act, to_torch_act
 
 pytestmark = pytest.mark.gpu
 
 LAYER_TOL = 2e-3  # max |y - y_oracle| / max |y_oracle| per row
 
 
-def run_and_check(L, x, act, grouped_min_tokens=6, max_tokens=None, decode_impl=0, math=0, bf16_excess=1.0):
+def run_and_check(L, x, act, grouped_min_tokens=6, max_tokens=None, decode_impl=0, math=0):
     M = x.shape[0]
     layer = gpu_layer(L, act, max_tokens or M, grouped_min_tokens, decode_impl=decode_impl, math=math)
     y = layer.forward(to_torch_act(x))
@@ -35,12 +35,14 @@ def run_and_check(L, x, act, grouped_min_tokens=6, max_tokens=None, decode_impl=
     got, want = oracle.to_f32(to_np_act(y)), oracle.to_f32(yref)
     assert np.isfinite(got).all()
     e = rel_err_rows(got[keep], want[keep])
-    if act == oracle.BF16:  # the output is rounded to BF16: allow one BF16 step of the element on top of the contract
-        assert bf16_rows_close(got[keep], want[keep], LAYER_TOL) <= bf16_excess, "layer error %.3g" % e
-        if bf16_excess > 1.0:  # nearly every element inside the plain allowance
-            rowmax = np.abs(want[keep]).max(axis=1, keepdims=True)
-            ulp = 2.0 ** (np.floor(np.log2(np.maximum(np.abs(want[keep]), 1e-30))) - 7)
-            assert (np.abs(got[keep] - want[keep]) <= LAYER_TOL * rowmax + ulp).mean() > 0.999
+    if act == oracle.BF16:
+        # A BF16 pipeline rounds gate, up, silu, h and y to BF16 (the reference's arithmetic). That alone puts the oracle o_t away
+        # from the evaluation that never rounds (FP32 activations, double accumulation), and two pipelines that round cannot agree
+        # closer than that. The GPU is judged against the unrounded evaluation: the contract plus half a BF16 step of the output's
+        # own rounding (2^-9 of the row maximum), or 1.25 x the oracle's own distance where that is larger.
+        truth = oracle.to_f32(oracle.moe_layer(oracle.bf16_to_f32(x), L)[0])
+        g_t, o_t = rel_err_rows(got[keep], truth[keep]), rel_err_rows(want[keep], truth[keep])
+        assert g_t <= max(LAYER_TOL + 2.0 ** -9, 1.25 * o_t), "GPU %.3g and oracle %.3g from the unrounded evaluation; GPU vs oracle %.3g" % (g_t, o_t, e)
     else:
         assert e < LAYER_TOL, "layer error %.3g" % e
     assert layer.probe("err", M).cpu().numpy().tolist() == [0] * 6
@@ -214,14 +216,32 @@ def test_prefill_tensor_core_path(act, router, G, shared, M):
     x = randn_act(np.random.default_rng(901 + M), (M, 512), act)
     before = sb.kernels.umma_abort_count()
     # FP32 activations: F16 operand rounding (2^-12 per value) stays far inside the 2e-3 contract. BF16 activations: the
-    # pipeline rounds gate, up, silu and h to BF16 like the FP32-math path, and a 1e-4 operand-rounding difference
-    # before such a rounding flips it to the neighbouring BF16 value (0.4-0.8 %) in a few percent of the h elements; the
-    # outputs then differ from the oracle's by up to twice the plain allowance in under 0.1 % of the elements.
-    layer, e = run_and_check(L, x, act, math=2, bf16_excess=2.0)
+    # pipeline rounds gate, up, silu and h to BF16 like the FP32-math path, and a 1e-4 operand-rounding difference before
+    # such a rounding flips it to the neighbouring BF16 value in a few percent of the h elements (see run_and_check).
+    layer, e = run_and_check(L, x, act, math=2)
     if act == oracle.F32:
         assert e < 1e-3
     assert sb.kernels.umma_abort_count() == before
     # twice through the same layer object: the persistent kernels leave no state behind
+    y1 = layer.forward(to_torch_act(x)).clone()
+    y2 = layer.forward(to_torch_act(x))
+    assert torch.equal(y1, y2)
+
+
+@pytest.mark.parametrize("act,router", [(oracle.BF16, "bf16"), (oracle.F32, "f32")])
+@pytest.mark.parametrize("M", (700, 1500))
+def test_prefill_tensor_core_path_with_hundreds_of_slots_per_expert(act, router, M):
+    # more than a 96-slot tile per expert on average: the 192-slot tile shape of the FFN kernels (single-buffered accumulators),
+    # full tiles, ragged last tiles, and with the routing skew experts of a few slots
+    import strixite_b200 as sb
+
+    L = make_layer(950 + M, d=512, I=256, E=6, k=3, G=128, router=router, shared="stacked", bias_sigma=1.5)
+    x = randn_act(np.random.default_rng(951 + M), (M, 512), act)
+    before = sb.kernels.umma_abort_count()
+    layer, e = run_and_check(L, x, act, math=2)
+    if act == oracle.F32:
+        assert e < 1e-3
+    assert sb.kernels.umma_abort_count() == before
     y1 = layer.forward(to_torch_act(x)).clone()
     y2 = layer.forward(to_torch_act(x))
     assert torch.equal(y1, y2)
