@@ -301,13 +301,13 @@ int strix_moe_stack_forward(strix_moe_layer *const *layers, int64_t n_layers, vo
 /* The expert half of the layer for expert-parallel runs, one call per batch of routed slots that arrived on this
  * device: ids[n] is each slot's expert in THIS layer's stacks (0 .. Estack - 1) and its activation row is
  * rows[row_index[i], :] (the layer's activation dtype), or rows[i, :] when row_index is NULL - with row_index a token
- * routed to several local experts is sent once. partial[i, :] = W_down[ids[i]] * SwiGLU(W_gate_up[ids[i]] * row) in FP32,
- * without the routing coefficient. Groups the slots by expert and runs the tensor-core kernels; needs a layer created
+ * routed to several local experts is sent once. partial[i, :] = W_down[ids[i]] * SwiGLU(W_gate_up[ids[i]] * row), FP32
+ * [n, d] or (partial_f16 != 0) F16 [n, d] - one rounding of each FP32 sum, half the bytes - without the routing coefficient. Groups the slots by expert and runs the tensor-core kernels; needs a layer created
  * with math != STRIX_MATH_F32 over uniform 4-bit stacks, and n <= max_tokens * (k + shared). Slots with an invalid id
  * raise the expert error words and are left unwritten; an id of -2 marks an absent slot (padding of a fixed-capacity list):
  * skipped without an error. No counterpart in the reference (which has no expert parallelism). */
 int strix_moe_layer_experts_partial(strix_moe_layer *layer, const void *rows, const int32_t *row_index, const int32_t *ids,
-                                    int64_t n, float *partial, void *stream);
+                                    int64_t n, void *partial, int partial_f16, void *stream);
 /* The ordered weighted sum of the reference's combine (kernels/moe_grouped.hpp:60-62, second half): y[m, :] = sum over a
  * ascending of coef[m, a] * partial[m * A + a, :], one rounding; a token with an id outside [0, E) gets a NaN row.
  * pos (optional, [M * A]): slot (m, a) is row pos[m * A + a] of partial instead of row m * A + a - partial rows that
@@ -336,8 +336,9 @@ int strix_ep_gather_rows(const void *x, int64_t d, int act, const int32_t *rowto
  * slot_ids (-2 = absent, beyond a pair's count) and slot_row (the slot's row among the P * C received rows). */
 int strix_ep_unpack(const int32_t *meta_recv, int P, int64_t C, int64_t Cs, int32_t *slot_ids, int32_t *slot_row,
                     void *stream);
-/* Expert rank: summed[s, i, :] = sum over row (s, i)'s slots, in slot order, of coef * partial[slot, :] (FP32). */
-int strix_ep_row_sum(const float *partial, const int32_t *meta_recv, int P, int64_t C, int64_t Cs, int64_t d,
+/* Expert rank: summed[s, i, :] = sum over row (s, i)'s slots, in slot order, of coef * partial[slot, :] (FP32 sums of FP32 or,
+ * with partial_f16, F16 partials - what strix_moe_layer_experts_partial wrote). */
+int strix_ep_row_sum(const void *partial, int partial_f16, const int32_t *meta_recv, int P, int64_t C, int64_t Cs, int64_t d,
                      float *summed, void *stream);
 /* Home rank: y[t, :] = the returned rows back[r, pos[t, r], :] added in ascending r, rounded once to `act`; NaN for a token
  * with an id outside [0, E]. */

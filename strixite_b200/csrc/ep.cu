@@ -11,6 +11,8 @@
 // Everything is in token order per destination, so the layout is a pure function of the routing.
 #include "common.cuh"
 
+#include <cuda_fp16.h>
+
 #include "strixite_b200.h"
 
 namespace {
@@ -173,7 +175,8 @@ __global__ void __launch_bounds__(256) ep_unpack_kernel(const int32_t *meta, int
 
 // Expert side: summed[s][i][:] = sum over the row's slots, in slot order, of coef * partial[slot][:] (FP32, fmaf as the
 // reference's combine, strixite kernels/moe_grouped.hip:456-472). One block per received row.
-__global__ void __launch_bounds__(256) ep_row_sum_kernel(const float4 *partial, const int32_t *meta, int C, int Cs, int d4, float4 *summed) {
+template <bool H>  // H: the partial sums are F16 (strix_moe_layer_experts_partial with partial_f16), else FP32
+__global__ void __launch_bounds__(256) ep_row_sum_kernel(const void *partial, const int32_t *meta, int C, int Cs, int d4, float4 *summed) {
     const int s = blockIdx.y, i = blockIdx.x;
     const int32_t *m = meta + (int64_t)s * (4 + 2 * C + 3 * Cs);
     if (i >= m[0]) return;
@@ -183,7 +186,15 @@ __global__ void __launch_bounds__(256) ep_row_sum_kernel(const float4 *partial, 
         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
         for (int q = 0; q < n; ++q) {
             const float c = __int_as_float(sm[3 * q + 2]);
-            const float4 p = partial[((int64_t)s * Cs + first + q) * d4 + j];
+            const int64_t e = ((int64_t)s * Cs + first + q) * d4 + j;
+            float4 p;
+            if constexpr (H) {
+                const uint2 u = static_cast<const uint2 *>(partial)[e];
+                const float2 lo = __half22float2(*reinterpret_cast<const __half2 *>(&u.x)), hi = __half22float2(*reinterpret_cast<const __half2 *>(&u.y));
+                p = make_float4(lo.x, lo.y, hi.x, hi.y);
+            } else {
+                p = static_cast<const float4 *>(partial)[e];
+            }
             v.x = fmaf(c, p.x, v.x), v.y = fmaf(c, p.y, v.y), v.z = fmaf(c, p.z, v.z), v.w = fmaf(c, p.w, v.w);
         }
         summed[((int64_t)s * C + i) * d4 + j] = v;
@@ -260,12 +271,14 @@ int strix_ep_unpack(const int32_t *meta_recv, int P, int64_t C, int64_t Cs, int3
     return 0;
 }
 
-int strix_ep_row_sum(const float *partial, const int32_t *meta_recv, int P, int64_t C, int64_t Cs, int64_t d, float *summed, void *stream) {
+int strix_ep_row_sum(const void *partial, int partial_f16, const int32_t *meta_recv, int P, int64_t C, int64_t Cs, int64_t d, float *summed, void *stream) {
     const char *fn = "ep_row_sum";
     SB_CHECK(partial && meta_recv && summed, fn, ": null pointer");
     SB_CHECK(P >= 1 && P <= kMaxRanks && C >= 1 && Cs >= 1 && d >= 4 && d % 4 == 0 && aligned16(partial) && aligned16(summed), fn, ": P = ", P, ", C = ", C, ", d = ", d);
-    ep_row_sum_kernel<<<dim3((unsigned)C, (unsigned)P), 256, 0, static_cast<cudaStream_t>(stream)>>>(reinterpret_cast<const float4 *>(partial), meta_recv, (int)C, (int)Cs,
-                                                                                                  (int)(d / 4), reinterpret_cast<float4 *>(summed));
+    const dim3 grid((unsigned)C, (unsigned)P);
+    auto st = static_cast<cudaStream_t>(stream);
+    if (partial_f16) ep_row_sum_kernel<true><<<grid, 256, 0, st>>>(partial, meta_recv, (int)C, (int)Cs, (int)(d / 4), reinterpret_cast<float4 *>(summed));
+    else ep_row_sum_kernel<false><<<grid, 256, 0, st>>>(partial, meta_recv, (int)C, (int)Cs, (int)(d / 4), reinterpret_cast<float4 *>(summed));
     SB_LAUNCH_OK(fn);
     return 0;
 }

@@ -11,6 +11,8 @@
 #include <mutex>
 #include "common.cuh"
 
+#include <cuda_fp16.h>
+
 #include "grouped.cuh"
 #include "prefill_umma.cuh"
 #include "strixite_b200.h"
@@ -324,9 +326,22 @@ __global__ void __launch_bounds__(256)
 }
 
 // The same on four consecutive outputs per thread: 16-byte loads of the partial rows, four of them in flight per step.
-template <typename T>
+// Four consecutive partial sums from element `elem` on: FP32, or F16 (the layer's own tensor-core path stores its per-slot
+// sums as F16 - half the traffic of the combine; the public grouped entries keep the caller's FP32 buffer).
+template <bool H>
+__device__ __forceinline__ float4 ld_partial4(const void *partial, int64_t elem) {
+    if constexpr (H) {
+        const uint2 u = __ldcs(reinterpret_cast<const uint2 *>(static_cast<const __half *>(partial) + elem));
+        const float2 lo = __half22float2(*reinterpret_cast<const __half2 *>(&u.x)), hi = __half22float2(*reinterpret_cast<const __half2 *>(&u.y));
+        return make_float4(lo.x, lo.y, hi.x, hi.y);
+    } else {
+        return __ldcs(reinterpret_cast<const float4 *>(static_cast<const float *>(partial) + elem));
+    }
+}
+
+template <typename T, bool H>
 __global__ void __launch_bounds__(256)
-    combine_reduce4_kernel(const float *partial, const int64_t *pos, const int32_t *ids, const float *coef, int64_t M, int64_t A, int64_t E,
+    combine_reduce4_kernel(const void *partial, const int64_t *pos, const int32_t *ids, const float *coef, int64_t M, int64_t A, int64_t E,
                            int64_t N, T *y) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, N4 = N / 4;
     if (i >= M * N4) return;
@@ -335,7 +350,7 @@ __global__ void __launch_bounds__(256)
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
     if (pos != nullptr) {  // slot (m, a) lives in row pos[m * A + a] of partial
         for (int64_t a = 0; a < A; ++a) {
-            const float4 p = __ldcs(reinterpret_cast<const float4 *>(partial + pos[m * A + a] * N + n));
+            const float4 p = ld_partial4<H>(partial, pos[m * A + a] * N + n);
             const float c = coef[m * A + a];
             const int32_t id = ids[m * A + a];
             ok = ok && id >= 0 && id < E;
@@ -345,14 +360,14 @@ __global__ void __launch_bounds__(256)
         st_act(y, m * N + n, ok ? v.x : q), st_act(y, m * N + n + 1, ok ? v.y : q), st_act(y, m * N + n + 2, ok ? v.z : q), st_act(y, m * N + n + 3, ok ? v.w : q);
         return;
     }
-    const float *row = partial + m * A * N + n;
+    const int64_t row = m * A * N + n;
     int64_t a = 0;
     for (; a + 4 <= A; a += 4) {
         float4 p[4];
         float c[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            p[j] = __ldcs(reinterpret_cast<const float4 *>(row + (a + j) * N));
+            p[j] = ld_partial4<H>(partial, row + (a + j) * N);
             c[j] = coef[m * A + a + j];
             const int32_t id = ids[m * A + a + j];
             ok = ok && id >= 0 && id < E;
@@ -361,7 +376,7 @@ __global__ void __launch_bounds__(256)
         for (int j = 0; j < 4; ++j) v.x = fmaf(c[j], p[j].x, v.x), v.y = fmaf(c[j], p[j].y, v.y), v.z = fmaf(c[j], p[j].z, v.z), v.w = fmaf(c[j], p[j].w, v.w);
     }
     for (; a < A; ++a) {
-        const float4 p = __ldcs(reinterpret_cast<const float4 *>(row + a * N));
+        const float4 p = ld_partial4<H>(partial, row + a * N);
         const float c = coef[m * A + a];
         const int32_t id = ids[m * A + a];
         ok = ok && id >= 0 && id < E;
@@ -463,18 +478,24 @@ int combine_grouped(const char *fn, const void *h, const StackView &w, int64_t E
     return 0;
 }
 
-int combine_reduce(const char *fn, const float *partial, const int32_t *ids, const float *coef, int64_t M, int64_t A, int64_t E, int64_t N,
-                   void *y, int act, cudaStream_t st, const int64_t *pos) {
+int combine_reduce(const char *fn, const void *partial, const int32_t *ids, const float *coef, int64_t M, int64_t A, int64_t E, int64_t N,
+                   void *y, int act, cudaStream_t st, const int64_t *pos, bool half_partial) {
     const bool vec = N % 4 == 0 && reinterpret_cast<uintptr_t>(partial) % 16 == 0 && reinterpret_cast<uintptr_t>(y) % 16 == 0;
-    SB_CHECK(pos == nullptr || vec, fn, ": the indexed combine needs N % 4 == 0 and 16-byte aligned buffers");
+    SB_CHECK((pos == nullptr && !half_partial) || vec, fn, ": the indexed combine and F16 partial sums need N % 4 == 0 and 16-byte aligned buffers");
     if (vec) {
         const unsigned blocks = (unsigned)((M * (N / 4) + 255) / 256);
-        if (act == kF32) combine_reduce4_kernel<float><<<blocks, 256, 0, st>>>(partial, pos, ids, coef, M, A, E, N, (float *)y);
-        else combine_reduce4_kernel<uint16_t><<<blocks, 256, 0, st>>>(partial, pos, ids, coef, M, A, E, N, (uint16_t *)y);
+        if (half_partial) {
+            if (act == kF32) combine_reduce4_kernel<float, true><<<blocks, 256, 0, st>>>(partial, pos, ids, coef, M, A, E, N, (float *)y);
+            else combine_reduce4_kernel<uint16_t, true><<<blocks, 256, 0, st>>>(partial, pos, ids, coef, M, A, E, N, (uint16_t *)y);
+        } else {
+            if (act == kF32) combine_reduce4_kernel<float, false><<<blocks, 256, 0, st>>>(partial, pos, ids, coef, M, A, E, N, (float *)y);
+            else combine_reduce4_kernel<uint16_t, false><<<blocks, 256, 0, st>>>(partial, pos, ids, coef, M, A, E, N, (uint16_t *)y);
+        }
     } else {
         const unsigned blocks = (unsigned)((M * N + 255) / 256);
-        if (act == kF32) combine_reduce_kernel<float><<<blocks, 256, 0, st>>>(partial, ids, coef, M, A, E, N, (float *)y);
-        else combine_reduce_kernel<uint16_t><<<blocks, 256, 0, st>>>(partial, ids, coef, M, A, E, N, (uint16_t *)y);
+        const float *pf = static_cast<const float *>(partial);
+        if (act == kF32) combine_reduce_kernel<float><<<blocks, 256, 0, st>>>(pf, ids, coef, M, A, E, N, (float *)y);
+        else combine_reduce_kernel<uint16_t><<<blocks, 256, 0, st>>>(pf, ids, coef, M, A, E, N, (uint16_t *)y);
     }
     SB_LAUNCH_OK(fn, " reduce ", act_name(act), " M=", M, " A=", A, " N=", N);
     return 0;

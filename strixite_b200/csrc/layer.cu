@@ -332,8 +332,10 @@ int strix_moe_layer_forward(strix_moe_layer *L, const void *x, int64_t M, void *
         // many tokens on the tensor cores: bucket-ordered F16 activations, gate/up with SwiGLU in its epilogue, down into
         // FP32 partials, then the ordered reduction of the reference's combine
         SB_TRY(sb::group_routes_multi(fn, L->ids, M * A, L->Estack, static_cast<int32_t *>(L->group_ws), L->route_scratch, expert_err, false, st));
-        SB_TRY(sb::prefill_experts(L->prefill, x, nullptr, act, static_cast<const int32_t *>(L->group_ws), M, A, L->partial, st));
-        SB_TRY(sb::combine_reduce(fn, L->partial, L->ids, L->coef, M, A, L->Estack, d.d, y, act, st));
+        // the per-slot sums between the down projection and the combine are F16 here: one more rounding of 2^-11 on values the
+        // contract allows 2e-3 on, for half the bytes written and read back (the buffer is the FP32-sized one of the grouped path)
+        SB_TRY(sb::prefill_experts(L->prefill, x, nullptr, act, static_cast<const int32_t *>(L->group_ws), M, A, L->partial, true, st));
+        SB_TRY(sb::combine_reduce(fn, L->partial, L->ids, L->coef, M, A, L->Estack, d.d, y, act, st, nullptr, true));
     } else if (M >= d.grouped_min_tokens) {
         SB_TRY(strix_moe_group_routes(L->ids, M, A, L->Estack, L->group_ws, L->group_ws_bytes, expert_err, stream));
         if (d.experts_mixed) {
@@ -372,8 +374,8 @@ int strix_moe_layer_forward(strix_moe_layer *L, const void *x, int64_t M, void *
     return 0;
 }
 
-int strix_moe_layer_experts_partial(strix_moe_layer *L, const void *rows, const int32_t *row_index, const int32_t *ids, int64_t n, float *partial,
-                                    void *stream) {
+int strix_moe_layer_experts_partial(strix_moe_layer *L, const void *rows, const int32_t *row_index, const int32_t *ids, int64_t n, void *partial,
+                                    int partial_f16, void *stream) {
     const char *fn = "moe_layer_experts_partial";
     SB_CHECK(L != nullptr && rows != nullptr && ids != nullptr && partial != nullptr, fn, ": null pointer");
     SB_CHECK(L->prefill != nullptr, fn, ": the layer has no tensor-core plan (needs math != F32, uniform 4-bit stacks, d % 256 == 0, I % 128 == 0 and max_tokens >= tensor_min_tokens)");
@@ -381,7 +383,7 @@ int strix_moe_layer_experts_partial(strix_moe_layer *L, const void *rows, const 
     auto st = static_cast<cudaStream_t>(stream);
     // ids of -2 are absent slots (the padding of a fixed-capacity slot list): no error, never computed
     SB_TRY(sb::group_routes_multi(fn, ids, n, L->Estack, static_cast<int32_t *>(L->group_ws), L->route_scratch, L->err + 3, true, st));
-    SB_TRY(sb::prefill_experts(L->prefill, rows, row_index, L->d.act, static_cast<const int32_t *>(L->group_ws), n, 1, partial, st));
+    SB_TRY(sb::prefill_experts(L->prefill, rows, row_index, L->d.act, static_cast<const int32_t *>(L->group_ws), n, 1, partial, partial_f16 != 0, st));
     return 0;
 }
 

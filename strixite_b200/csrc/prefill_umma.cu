@@ -39,6 +39,8 @@
 #include "prefill_umma.cuh"
 #include "umma.cuh"
 
+#include <cstdlib>
+
 namespace {
 
 using namespace sb;
@@ -101,6 +103,9 @@ struct FC {
     static constexpr int AccCols = TileSlots, BufCols = NAcc * AccCols, AColBase = AccBufs * BufCols;
     static constexpr int AS = SMALL ? 4 : 2;                  // A stages in tensor memory
     static constexpr int EpiWarps = SMALL ? 4 : 8;
+    // XWIDE: nothing else can run while the single accumulator set drains, so the dequantizer warps take their share of it
+    static constexpr bool CoopEpi = XW;
+    static constexpr int DrainWarps = EpiWarps + (CoopEpi ? kDequantWarps : 0);  // warps that arrive on acc_empty
     static constexpr int ProducerWarp = kDequantWarps + EpiWarps, MmaWarp = ProducerWarp + 1;  // NAcc issuing warps from MmaWarp on
     static constexpr int Threads = (MmaWarp + NAcc) * 32;
     static_assert(AColBase + AS * kAStageCols <= 512, "tensor memory has 512 columns");
@@ -164,20 +169,25 @@ struct FfnArgs {
     const uint16_t *scale, *minv;  // [stack rows, K / G]
     int K, rows_per_expert, I, RB;
     uint16_t *hs;    // MODE 0 output: [S, I] F16, 8-groups in the order 0,4,1,5,2,6,3,7
-    float *partial;  // MODE 1 output: [S, N] by slot
+    void *partial;   // MODE 1 output: [S, N] by slot, FP32 or (partial_f16) F16
+    int partial_f16;
     int N;
     int bf16_act;    // MODE 0: round gate, up and the product as a BF16 activation pipeline does
 };
 
 __device__ __forceinline__ float bf16_rn(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
-// SwiGLU of one output with the reference's own operations (expf and an IEEE divide, strixite kernels/swiglu.hip:22); a BF16
-// activation pipeline rounds gate, up, silu(gate) and the product (strixite kernels/swiglu.hpp:21).
+// SwiGLU of one output; a BF16 activation pipeline rounds gate, up, silu(gate) and the product (strixite kernels/swiglu.hpp:21).
+// exp and the divide are the hardware approximations (__expf: 2 ulp + the range reduction's error; __fdividef: 2 ulp; the
+// reference uses expf and an IEEE divide, kernels/swiglu.hip:22): the result is rounded to F16 (2^-11) or BF16 (2^-8) right
+// after, far coarser than the 4 ulp of FP32, and in the 192-slot tile shape the epilogue is on the critical path (it drains
+// the only accumulator set), where the exact forms cost 3x the instructions. |g| > 87 (where __fdividef's range limit on the
+// denominator could matter) gives silu = g or -0 in both forms.
 __device__ __forceinline__ float swiglu_rounded(float g, float u, bool bf16) {
     if (bf16) {
         g = bf16_rn(g), u = bf16_rn(u);
-        return bf16_rn(bf16_rn(g / (1.0f + expf(-g))) * u);
+        return bf16_rn(bf16_rn(__fdividef(g, 1.0f + __expf(-g))) * u);
     }
-    return g / (1.0f + expf(-g)) * u;
+    return __fdividef(g, 1.0f + __expf(-g)) * u;
 }
 
 template <int MODE, int G, int SHAPE>
@@ -195,7 +205,7 @@ __global__ void __launch_bounds__(FC<SHAPE>::Threads, 1)
         // full[kc % BS]: K block kc is ready = its token tile has landed (the producer's arrival + bytes) and the 8 dequantizer
         // warps of its half have stored the A stage; consumed[kc % BS]: every issuing warp has committed its MMAs of K block kc
         for (int i = 0; i < C::BS; ++i) mbar_init(&ctl.full[i], 1 + kDequantWarps / 2), mbar_init(&ctl.consumed[i], C::NAcc);
-        for (int i = 0; i < 2; ++i) mbar_init(&ctl.acc_full[i], C::NAcc), mbar_init(&ctl.acc_empty[i], C::EpiWarps);
+        for (int i = 0; i < 2; ++i) mbar_init(&ctl.acc_full[i], C::NAcc), mbar_init(&ctl.acc_empty[i], C::DrainWarps);
         ctl.abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -214,6 +224,70 @@ __global__ void __launch_bounds__(FC<SHAPE>::Threads, 1)
     // stack row of row half `acc`, row 0, of a work item
     auto first_row = [&](int bucket, int rb, int acc) {
         return MODE == 0 ? bucket * a.rows_per_expert + acc * a.I + rb * kTileM : bucket * a.rows_per_expert + rb * 2 * kTileM + acc * kTileM;
+    };
+
+    // The epilogue of work item w (the it-th of this CTA) for one warp: its lane quadrant q (= warp % 4, the tensor-memory
+    // lanes a warp may read) and every per_q-th 16-column chunk from chunk j on. Returns false when a wait was abandoned.
+    const RouteTables rtab = route_tables(a.ws, a.ws[1], a.ws[2]);
+    auto drain_item = [&](int w, uint32_t it, int q, int j, int per_q, long long *waited) -> bool {
+        const int r = q * 32 + lane;
+        const int32_t *t = a.tiles + 1 + 3 * (w / a.RB);
+        const int rb = w % a.RB, start = t[1], n_valid = t[2];
+        const uint32_t buf = it % C::AccBufs;
+        bool ok = true;
+        TIMED_WAIT(0, mbar_wait(&ctl.acc_full[buf], (it / C::AccBufs) & 1u, abort_flag));
+        if (!ok) return false;
+        tc_fence_after();
+        const uint32_t tbase = tmem + ((uint32_t)(q * 32) << 16) + buf * C::BufCols;
+        for (int c0 = j * 16; c0 < n_valid; c0 += per_q * 16) {
+            uint32_t v0[16], v1[16];
+            tmem_ld16(tbase + c0, v0);
+            tmem_ld16(tbase + C::KSplit * C::AccCols + c0, v1);
+            tmem_ld_wait();
+            if constexpr (C::KSplit == 2) {  // the second K part of each row half, added in a fixed order
+                uint32_t w0[16], w1[16];
+                tmem_ld16(tbase + C::AccCols + c0, w0);
+                tmem_ld16(tbase + 3 * C::AccCols + c0, w1);
+                tmem_ld_wait();
+#pragma unroll
+                for (int jj = 0; jj < 16; ++jj) {
+                    v0[jj] = __float_as_uint(__uint_as_float(v0[jj]) + __uint_as_float(w0[jj]));
+                    v1[jj] = __float_as_uint(__uint_as_float(v1[jj]) + __uint_as_float(w1[jj]));
+                }
+            }
+            if (MODE == 0) {
+                const int i = rb * kTileM + r;  // intermediate column
+                const int pos = (i & ~7) + ((i & 3) << 1) + ((i >> 2) & 1);
+#pragma unroll
+                for (int jj = 0; jj < 16; ++jj) {
+                    if (c0 + jj < n_valid) {
+                        const float h = swiglu_rounded(__uint_as_float(v0[jj]), __uint_as_float(v1[jj]), a.bf16_act != 0);
+                        a.hs[(int64_t)(start + c0 + jj) * a.I + pos] = __half_as_ushort(__float2half_rn(h));
+                    }
+                }
+            } else {
+                const int n = rb * 2 * kTileM + r;
+#pragma unroll
+                for (int jj = 0; jj < 16; ++jj) {
+                    if (c0 + jj < n_valid) {
+                        const int64_t o = (int64_t)rtab.slots[start + c0 + jj] * a.N + n;
+                        if (a.partial_f16) {
+                            __half *dst = static_cast<__half *>(a.partial) + o;
+                            dst[0] = __float2half_rn(__uint_as_float(v0[jj]));
+                            dst[kTileM] = __float2half_rn(__uint_as_float(v1[jj]));
+                        } else {
+                            float *dst = static_cast<float *>(a.partial) + o;
+                            dst[0] = __uint_as_float(v0[jj]);
+                            dst[kTileM] = __uint_as_float(v1[jj]);
+                        }
+                    }
+                }
+            }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ctl.acc_empty[buf]);
+        return true;
     };
 
     if (warp == C::ProducerWarp) {
@@ -296,6 +370,7 @@ __global__ void __launch_bounds__(FC<SHAPE>::Threads, 1)
         const int gpr = a.K / G;
         constexpr int NG = G >= 64 ? 1 : 64 / G;  // groups in a thread's 64 codes
         uint32_t rawc = 0;
+        [[maybe_unused]] uint32_t item = 0;
         bool ok = true;
         [[maybe_unused]] long long waited[2] = {0, 0};
         [[maybe_unused]] const long long t_start = PROFILE_CLOCK();
@@ -340,6 +415,11 @@ __global__ void __launch_bounds__(FC<SHAPE>::Threads, 1)
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&ctl.full[kc % C::BS]);
             }
+            if constexpr (C::CoopEpi) {  // this item's weights are all stored: help drain its accumulators
+                [[maybe_unused]] long long w_epi[1] = {0};
+                if (ok) ok = drain_item(w, item, warp & 3, C::EpiWarps / 4 + (warp >> 2), C::DrainWarps / 4, w_epi);
+                ++item;
+            }
         }
         if (tid == 0) {
             PROFILE_ADD(6, waited[0]);
@@ -347,64 +427,14 @@ __global__ void __launch_bounds__(FC<SHAPE>::Threads, 1)
             PROFILE_ADD(8, (PROFILE_CLOCK() - t_start));
         }
     } else {
-        // ---- epilogue: lane quadrant q = warp % 4; with 8 warps the two of a quadrant take alternate 16-column chunks ----
-        const int ew = warp - kDequantWarps, q = ew & 3, half = ew >> 2, r = q * 32 + lane;
-        constexpr int ChunkStride = 16 * (C::EpiWarps / 4);
-        const RouteTables rtab = route_tables(a.ws, a.ws[1], a.ws[2]);
+        // ---- epilogue warps: lane quadrant q = warp % 4; the warps of a quadrant take alternate 16-column chunks ----
+        const int ew = warp - kDequantWarps;
+        constexpr int PerQ = C::DrainWarps / 4;
         uint32_t it = 0;
         bool ok = true;
         [[maybe_unused]] long long waited[1] = {0};
         [[maybe_unused]] const long long t_start = PROFILE_CLOCK();
-        for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x, ++it) {
-            const int32_t *t = a.tiles + 1 + 3 * (w / a.RB);
-            const int rb = w % a.RB, start = t[1], n_valid = t[2];
-            const uint32_t buf = it % C::AccBufs;
-            TIMED_WAIT(0, mbar_wait(&ctl.acc_full[buf], (it / C::AccBufs) & 1u, abort_flag));
-            if (!ok) break;
-            tc_fence_after();
-            const uint32_t tbase = tmem + ((uint32_t)(q * 32) << 16) + buf * C::BufCols;
-            for (int c0 = half * 16; c0 < n_valid; c0 += ChunkStride) {
-                uint32_t v0[16], v1[16];
-                tmem_ld16(tbase + c0, v0);
-                tmem_ld16(tbase + C::KSplit * C::AccCols + c0, v1);
-                tmem_ld_wait();
-                if constexpr (C::KSplit == 2) {  // the second K part of each row half, added in a fixed order
-                    uint32_t w0[16], w1[16];
-                    tmem_ld16(tbase + C::AccCols + c0, w0);
-                    tmem_ld16(tbase + 3 * C::AccCols + c0, w1);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        v0[j] = __float_as_uint(__uint_as_float(v0[j]) + __uint_as_float(w0[j]));
-                        v1[j] = __float_as_uint(__uint_as_float(v1[j]) + __uint_as_float(w1[j]));
-                    }
-                }
-                if (MODE == 0) {
-                    const int i = rb * kTileM + r;  // intermediate column
-                    const int pos = (i & ~7) + ((i & 3) << 1) + ((i >> 2) & 1);
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        if (c0 + j < n_valid) {
-                            const float h = swiglu_rounded(__uint_as_float(v0[j]), __uint_as_float(v1[j]), a.bf16_act != 0);
-                            a.hs[(int64_t)(start + c0 + j) * a.I + pos] = __half_as_ushort(__float2half_rn(h));
-                        }
-                    }
-                } else {
-                    const int n = rb * 2 * kTileM + r;
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        if (c0 + j < n_valid) {
-                            float *dst = a.partial + (int64_t)rtab.slots[start + c0 + j] * a.N + n;
-                            dst[0] = __uint_as_float(v0[j]);
-                            dst[kTileM] = __uint_as_float(v1[j]);
-                        }
-                    }
-                }
-            }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&ctl.acc_empty[buf]);
-        }
+        for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x, ++it) ok = drain_item(w, it, ew & 3, ew >> 2, PerQ, waited);
         if (tid == kDequantWarps * 32) {
             PROFILE_ADD(9, waited[0]);
             PROFILE_ADD(10, (PROFILE_CLOCK() - t_start));
@@ -672,12 +702,15 @@ bool dense_bf16_ok(const void *x, const void *w, int64_t M, int64_t N, int64_t K
            reinterpret_cast<uintptr_t>(w) % 16 == 0;
 }
 
-int prefill_experts(PrefillPlan *p, const void *x, const int32_t *row_index, int act, const int32_t *ws, int64_t M, int64_t A, float *partial,
-                    cudaStream_t st) {
+int prefill_experts(PrefillPlan *p, const void *x, const int32_t *row_index, int act, const int32_t *ws, int64_t M, int64_t A, void *partial,
+                    bool half_partial, cudaStream_t st) {
     const char *fn = "moe_layer_forward (tensor-core experts)";
     // a handful of tokens (decode, verify): tiles of 32 slots and four issuing warps; many tokens: tiles of 96 slots; an average
     // of more than a 96-slot tile per expert: tiles of 192 slots
-    const int shape = M * A <= kSmallSlots ? kSmall : M * A > (int64_t)FC<kWide>::TileSlots * p->Estack ? kXWide : kWide;
+    int shape = M * A <= kSmallSlots ? kSmall : M * A > (int64_t)FC<kWide>::TileSlots * p->Estack ? kXWide : kWide;
+#ifdef STRIX_PROFILE
+    if (const char *force = std::getenv("STRIX_FFN_SHAPE")) shape = std::atoi(force);  // diagnostic build: A/B of the tile shapes
+#endif
     SB_CHECK(M * A <= p->max_tokens * p->A, fn, ": ", M * A, " slots exceed the layer's ", p->max_tokens * p->A);
     const int32_t S = (int32_t)(M * A), E = (int32_t)p->Estack;
     tiles_kernel<<<1, 1024, 0, st>>>(ws, p->tiles, shape == kSmall ? FC<kSmall>::TileSlots : shape == kXWide ? FC<kXWide>::TileSlots : FC<kWide>::TileSlots, S, E);
@@ -689,12 +722,12 @@ int prefill_experts(PrefillPlan *p, const void *x, const int32_t *row_index, int
     FfnArgs a{};
     a.ws = ws, a.tiles = p->tiles;
     a.scale = p->gu_scale, a.minv = p->gu_min, a.K = (int)p->d, a.rows_per_expert = (int)(2 * p->I), a.I = (int)p->I, a.RB = (int)(p->I / kTileM);
-    a.hs = p->hs, a.partial = nullptr, a.N = 0, a.bf16_act = act == kBF16;
+    a.hs = p->hs, a.partial = nullptr, a.partial_f16 = 0, a.N = 0, a.bf16_act = act == kBF16;
     if (shape == kSmall) SB_TRY((launch_ffn<0, kSmall>(fn, p->G_gu, p->gu_raw, p->xg_map_s, a, p->sms, st)));
     else if (shape == kXWide) SB_TRY((launch_ffn<0, kXWide>(fn, p->G_gu, p->gu_raw, p->xg_map_x, a, p->sms, st)));
     else SB_TRY((launch_ffn<0, kWide>(fn, p->G_gu, p->gu_raw, p->xg_map, a, p->sms, st)));
     a.scale = p->dn_scale, a.minv = p->dn_min, a.K = (int)p->I, a.rows_per_expert = (int)p->d, a.RB = (int)(p->d / (2 * kTileM));
-    a.hs = nullptr, a.partial = partial, a.N = (int)p->d;
+    a.hs = nullptr, a.partial = partial, a.partial_f16 = half_partial ? 1 : 0, a.N = (int)p->d;
     if (shape == kSmall) SB_TRY((launch_ffn<1, kSmall>(fn, p->G_dn, p->dn_raw, p->hs_map_s, a, p->sms, st)));
     else if (shape == kXWide) SB_TRY((launch_ffn<1, kXWide>(fn, p->G_dn, p->dn_raw, p->hs_map_x, a, p->sms, st)));
     else SB_TRY((launch_ffn<1, kWide>(fn, p->G_dn, p->dn_raw, p->hs_map, a, p->sms, st)));

@@ -20,8 +20,9 @@ int prefill_router_logits(PrefillPlan *p, const void *x, int64_t M, float *logit
 // Tiles -> bucket-ordered F16 activations -> gate/up + SwiGLU -> down: FP32 partial[slot, d] for every slot with a
 // valid expert. `ws` is the grouping workspace of moe_group_routes for (M, A, Estack).
 // Slot s reads activation row row_index[s], or s / A (one row per token) when row_index is null.
-int prefill_experts(PrefillPlan *p, const void *x, const int32_t *row_index, int act, const int32_t *ws, int64_t M, int64_t A, float *partial,
-                    cudaStream_t st);
+// half_partial: partial is F16 [slots, d] (one rounding of each FP32 sum; half the bytes to write and to combine) instead of FP32.
+int prefill_experts(PrefillPlan *p, const void *x, const int32_t *row_index, int act, const int32_t *ws, int64_t M, int64_t A, void *partial,
+                    bool half_partial, cudaStream_t st);
 // y[M, N] (FP32) = x[M, K] (BF16) * w[N, K]^T (BF16) + bias[n < n_bias] on the tensor cores; dense_bf16_ok says whether the
 // shape and alignment qualify (M >= 64, K % 64 == 0, 16-byte aligned pointers).
 bool dense_bf16_ok(const void *x, const void *w, int64_t M, int64_t N, int64_t K);
@@ -35,7 +36,8 @@ unsigned int prefill_ws_refusals();
 void prefill_cycles(unsigned long long *out, bool reset);
 
 // y[m, :] = sum_a coef[m, a] * partial[m * A + a, :] in ascending a; NaN rows for tokens with an invalid id (grouped.cu).
-int combine_reduce(const char *fn, const float *partial, const int32_t *ids, const float *coef, int64_t M, int64_t A, int64_t E, int64_t N,
-                   void *y, int act, cudaStream_t st, const int64_t *pos = nullptr);  // pos: slot (m, a) is row pos[m * A + a] of partial
+// pos: slot (m, a) is row pos[m * A + a] of partial; half_partial: the partial sums are F16 (prefill_experts with half_partial).
+int combine_reduce(const char *fn, const void *partial, const int32_t *ids, const float *coef, int64_t M, int64_t A, int64_t E, int64_t N,
+                   void *y, int act, cudaStream_t st, const int64_t *pos = nullptr, bool half_partial = false);
 
 }  // namespace sb

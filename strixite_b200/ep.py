@@ -202,7 +202,7 @@ class CudaBackend:
                 rowtok=z(world, self.Cr), meta_send=z(world, self.MW), meta_recv=z(world, self.MW), pos=z(Tc, world), flags=z(2),
                 plan_scratch=z(int(lib.strix_ep_plan_scratch_ints(Tc))),
                 rows_send=z(world, self.Cr, d, dt=adt), rows_recv=z(world, self.Cr, d, dt=adt), slot_ids=z(n_cap), slot_row=z(n_cap),
-                partial=torch.empty((n_cap, d), dtype=torch.float32, device=dev), summed=z(world, self.Cr, d, dt=torch.float32),
+                partial=torch.empty((n_cap, d), dtype=torch.float16, device=dev), summed=z(world, self.Cr, d, dt=torch.float32),
                 back=z(world, self.Cr, d, dt=torch.float32), y=torch.empty((Tc, d), dtype=adt, device=dev)))
         self.launches = 0
 
@@ -268,7 +268,7 @@ class CudaBackend:
         b["meta_last"] = meta_recv
         call("strix_ep_unpack", K._p(meta_recv), self.P, self.Cr, self.Cs, K._p(b["slot_ids"]), K._p(b["slot_row"]), self._sp(c))
         b["shard"].experts_partial(rows_recv.reshape(-1, self.d), b["slot_ids"], partial=b["partial"], stream=self.streams[c], row_index=b["slot_row"])
-        call("strix_ep_row_sum", K._p(b["partial"]), K._p(meta_recv), self.P, self.Cr, self.Cs, self.d, K._p(b["summed"]), self._sp(c))
+        call("strix_ep_row_sum", K._p(b["partial"]), 1 if b["partial"].dtype == torch.float16 else 0, K._p(meta_recv), self.P, self.Cr, self.Cs, self.d, K._p(b["summed"]), self._sp(c))
         self.launches += 9  # unpack, grouping (3), tiles, ordered rows, two FFN kernels, row sum
         return b["summed"]
 

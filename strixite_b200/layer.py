@@ -41,7 +41,7 @@ lib.strix_moe_layer_probe.argtypes = [C.c_void_p, C.c_char_p]
 lib.strix_moe_layer_probe.restype = C.c_void_p
 lib.strix_moe_layer_reset_errors.argtypes = [C.c_void_p, C.c_void_p]
 lib.strix_moe_layer_reset_errors.restype = C.c_int
-lib.strix_moe_layer_experts_partial.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p]
+lib.strix_moe_layer_experts_partial.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int, C.c_void_p]
 lib.strix_moe_layer_experts_partial.restype = C.c_int
 
 
@@ -110,12 +110,15 @@ class MoeLayer:
         return y_host
 
     def experts_partial(self, rows, ids, partial=None, stream=None, row_index=None):
-        """partial[i, :] = W_down[ids[i]] * SwiGLU(W_gate_up[ids[i]] * row_i) in FP32 for a batch of routed slots: the expert
-        half of an expert-parallel layer. row_i = rows[row_index[i]] (int32 index), or rows[i] when row_index is None."""
+        """partial[i, :] = W_down[ids[i]] * SwiGLU(W_gate_up[ids[i]] * row_i) for a batch of routed slots: the expert half of an
+        expert-parallel layer, FP32 or (a float16 `partial` tensor) F16. row_i = rows[row_index[i]] (int32 index), or rows[i]
+        when row_index is None."""
         n = ids.shape[0]
         partial = torch.empty((n, self.d), dtype=torch.float32, device=rows.device) if partial is None else partial
+        if partial.dtype not in (torch.float32, torch.float16):
+            raise StrixError("experts_partial: partial must be float32 or float16, got %s" % partial.dtype)
         call("strix_moe_layer_experts_partial", self._h, K._p(rows), None if row_index is None else K._p(row_index), K._p(ids), n, K._p(partial),
-             K._s(stream))
+             1 if partial.dtype == torch.float16 else 0, K._s(stream))
         return partial
 
     @property

@@ -82,6 +82,32 @@ def test_plan_kernel_matches_its_numpy_restatement(P, rank):
             assert np.array_equal(pos.cpu().numpy(), want[2])
 
 
+def test_experts_partial_f16_is_the_rounded_fp32_result():
+    """strix_moe_layer_experts_partial: the F16 partial sums are the FP32 ones rounded once, and both are the oracle's per-slot
+    expert outputs within the tensor-core contract."""
+    L, x = _layer(), _tokens()
+    layer = gpu_layer(L, oracle.BF16, T, math=2)
+    rng = np.random.default_rng(3)
+    n = 200
+    ids = rng.integers(0, E + 1, n).astype(np.int32)
+    ids[5] = -2  # an absent slot: skipped, no error
+    rows = rng.integers(0, T, n).astype(np.int32)
+    xt = to_torch_act(x)
+    p32 = torch.zeros((n, D), dtype=torch.float32, device="cuda")
+    p16 = torch.zeros((n, D), dtype=torch.float16, device="cuda")
+    layer.experts_partial(xt, torch.from_numpy(ids).cuda(), partial=p32, row_index=torch.from_numpy(rows).cuda())
+    layer.experts_partial(xt, torch.from_numpy(ids).cuda(), partial=p16, row_index=torch.from_numpy(rows).cuda())
+    torch.cuda.synchronize()
+    assert torch.equal(p32.to(torch.float16), p16)
+    assert layer.probe("err", 1).cpu().numpy().tolist() == [0] * 6
+    keep = ids >= 0
+    xs = np.ascontiguousarray(x[rows[keep]])
+    gid = ids[keep].reshape(-1, 1)
+    h, _ = oracle.experts_gather(xs, L["gate_up"], gid, swiglu=True)
+    want, _ = oracle.experts_combine(np.ascontiguousarray(h.reshape(-1, I)), L["down"], gid, np.ones((gid.shape[0], 1), np.float32))
+    assert rel_err_rows(p32.cpu().numpy()[keep], oracle.to_f32(want)) < 2e-3 + 2.0 ** -7  # BF16 pipeline: h rounded to BF16 by the oracle
+
+
 def _single_device(L, x):
     single = gpu_layer(L, oracle.BF16, T, math=2)
     return to_np_act(single.forward(to_torch_act(x)))
