@@ -25,6 +25,7 @@ every row for the small batches, a seeded sample of rows for the large ones (tok
 ids of ALL rows against the oracle's router run on the GPU-produced logits.
 """
 import argparse
+import datetime
 import json
 import os
 import subprocess
@@ -633,7 +634,8 @@ def run_ep(args, cfg, steps, warmup, rank, world, local, device, P, line, want_p
     from strixite_b200 import synth
 
     if world > 1 and not dist.is_initialized():
-        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device(device))
+        # a short timeout: a rank that leaves a collective alone ends the run with an error in minutes, not a silent wait
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device(device), timeout=datetime.timedelta(seconds=240))
     barrier = dist.barrier if world > 1 else (lambda: None)  # one rank: the same code, its exchanges are the identity
     d, I, E, k, T = cfg["d"], cfg["I"], cfg["E"], cfg["k"], cfg["M"]
     Tl = T // world
@@ -659,7 +661,7 @@ def run_ep(args, cfg, steps, warmup, rank, world, local, device, P, line, want_p
     del gu, dn
     torch.cuda.empty_cache()
     layer = EP.cuda_layer(d, I, E, k, K.Act.BF16, rw, bias, gu_l, dn_l, world, rank, max_local_tokens=Tl, placement=place,
-                          chunks=args.ep_chunks)
+                          chunks=args.ep_chunks, peer_stores=not args.ep_all_to_all)
     xs = []
     for r in range(cfg["ring"]):
         g.manual_seed(9000 + 17 * r)
@@ -708,7 +710,7 @@ def run_ep(args, cfg, steps, warmup, rank, world, local, device, P, line, want_p
     out = dict(value=T / step_s, unit="tokens/s", steps=steps, warmup=warmup, ms_per_step=ms / steps, clocks=clocks, dtype="bf16", scaling="strong")
     out["config"] = config_of("ep_prefill16384", cfg, world, "two token sets alternate; every step streams far more than the 126 MB L2")
     out["config"].update(parallelism="expert parallel x%d (%s placement of the experts over the ranks, tokens split evenly, shared expert replicated; %s; %d chunk(s) per step)"
-                         % (world, "contiguous" if args.ep_contiguous else "load-balanced", "one row per (token, rank), summed on the expert rank", layer.chunks),
+                         % (world, "contiguous" if args.ep_contiguous else "load-balanced", "one row per (token, rank), summed on the expert rank; " + ("exchange = peer stores of the gather and row-sum kernels over NVLink, F16 sums back, two barriers" if layer.backend.pushes else "exchange = all-to-alls, FP32 sums back" if world > 1 else "no exchange"), layer.chunks),
                          router_bias="Zipf(1.1)")
     out["e2e"] = dict(value=T * ke / float(dt.item()), unit="tokens/s", h2d_bytes_per_step=int(xh[0].numel() * 2 * world), d2h_bytes_per_step=int(yh.numel() * 2 * world),
                       steps=ke, note="pinned host tokens -> device -> expert-parallel layer -> pinned host outputs, per rank, wall clock, max over ranks")
@@ -722,9 +724,10 @@ def run_ep(args, cfg, steps, warmup, rank, world, local, device, P, line, want_p
     out["gpu_launches_per_step"] = layer.launches_per_step()
     out["gpu_launches"] = int(layer.launches_per_step() * steps)
     out["gpu_launches_note"] = "this library's kernels per step and rank (router, plan, grouping, tiles, gather, FFN, reduce), counted where they are enqueued; NCCL collectives come on top"
-    if rank == 0 and want_parity:
-        y = layer.forward(xs[0])
+    if want_parity:
+        y = layer.forward(xs[0])  # every rank: the forward exchanges tokens; only rank 0 then runs the oracle on its rows
         torch.cuda.synchronize()
+    if rank == 0 and want_parity:
         rows = np.sort(np.random.default_rng(5).choice(Tl, 64, replace=False))
         out["parity"] = parity_of(np.ascontiguousarray(host_act(xs[0])[rows]), np.ascontiguousarray(host_act(y)[rows]), [host_L], layer.last_logits().cpu().numpy(),
                                   layer.last_ids().cpu().numpy(), True, "64 of rank 0's %d rows (seeded sample; tokens are independent)" % Tl)
@@ -745,6 +748,7 @@ def main():
     ap.add_argument("--tensor-min-tokens", type=int, default=0, help="with --math 2: run forwards of at least this many tokens on the tensor-core path")
     ap.add_argument("--math", type=int, default=-1, choices=[-1, 0, 1, 2], help="override the workload's MoeMath (0 = FP32 kernels, 1/2 = tensor cores)")
     ap.add_argument("--ep-contiguous", action="store_true", help="expert parallel: experts e -> rank e / (E / N) instead of the load-balanced placement")
+    ap.add_argument("--ep-all-to-all", action="store_true", help="expert parallel: exchange through NCCL all-to-alls instead of the kernels' own peer stores")
     ap.add_argument("--ep-chunks", type=int, default=0, help="expert parallel: token chunks per step whose exchanges overlap the other chunk's kernels (0 = the default)")
     ap.add_argument("--grouped-min", type=int, default=0, help="override the token count from which the grouped expert path runs (reference: 6)")
     ap.add_argument("--decode-impl", type=int, default=0, choices=[0, 1], help="forwards of <= 8 tokens: 0 = the single streaming kernel, 1 = the per-function kernels")
@@ -825,7 +829,7 @@ def main():
     if world > 1:
         import torch.distributed as dist
 
-        dist.init_process_group("nccl", device_id=torch.device(device))
+        dist.init_process_group("nccl", device_id=torch.device(device), timeout=datetime.timedelta(seconds=240))
         barrier = lambda: dist.barrier()  # noqa: E731
     else:
         dist, barrier = None, (lambda: None)

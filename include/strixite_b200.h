@@ -340,10 +340,22 @@ int strix_ep_unpack(const int32_t *meta_recv, int P, int64_t C, int64_t Cs, int3
  * with partial_f16, F16 partials - what strix_moe_layer_experts_partial wrote). */
 int strix_ep_row_sum(const void *partial, int partial_f16, const int32_t *meta_recv, int P, int64_t C, int64_t Cs, int64_t d,
                      float *summed, void *stream);
-/* Home rank: y[t, :] = the returned rows back[r, pos[t, r], :] added in ascending r, rounded once to `act`; NaN for a token
- * with an id outside [0, E]. */
-int strix_ep_home_sum(const float *back, const int32_t *pos, const int32_t *ids, int64_t T, int64_t A, int64_t E, int P,
-                      int64_t C, int64_t d, void *y, int act, void *stream);
+/* Home rank: y[t, :] = the returned rows back[r, pos[t, r], :] (FP32, or F16 with back_f16) added in ascending r, rounded once to
+ * `act`; NaN for a token with an id outside [0, E]. */
+int strix_ep_home_sum(const void *back, int back_f16, const int32_t *pos, const int32_t *ids, int64_t T, int64_t A, int64_t E,
+                      int P, int64_t C, int64_t d, void *y, int act, void *stream);
+/* The exchange done by the kernels themselves, over memory the peers have mapped (NVLink peer stores) - no library all-to-all,
+ * no staging copy. `*_ptrs` are device arrays of P addresses: rank r's receive buffer as this GPU sees it ([P, C, d] rows,
+ * [P, MW] metadata, [P, C, d] returned sums; a rank's own entry is its local buffer). The ranks must meet at a barrier between
+ * a push and the kernels that read what was pushed.
+ *   strix_ep_push_rows     strix_ep_gather_rows with destination r's rows and the used part of its metadata block written into
+ *                          block [rank] of r's buffers
+ *   strix_ep_row_sum_push  strix_ep_row_sum with source s's sums written into block [rank] of s's `back` buffer, FP32 or
+ *                          (back_f16) F16 - one rounding of each FP32 sum, half the bytes on the links */
+int strix_ep_push_rows(const void *x, int64_t d, int act, const int32_t *rowtok, const int32_t *meta, int P, int rank, int64_t C,
+                       int64_t Cs, const uint64_t *rows_ptrs, const uint64_t *meta_ptrs, void *stream);
+int strix_ep_row_sum_push(const void *partial, int partial_f16, const int32_t *meta_recv, int P, int rank, int64_t C, int64_t Cs,
+                          int64_t d, const uint64_t *back_ptrs, int back_f16, void *stream);
 
 /* Device pointer of a named intermediate of the last forward - the reference's probes (runtime/qwen4exp.hpp:179-188):
  * "router_logits" f32 [M, E(+1)], "router_ids" i32 [M, A], "router_coef" f32 [M, A], "experts_h" [M, A, I],

@@ -98,7 +98,9 @@ SIGNATURES = {
     "strix_ep_gather_rows": [_vp, _i64, _int, _vp, _vp, _int, _i64, _i64, _vp, _vp],
     "strix_ep_unpack": [_vp, _int, _i64, _i64, _vp, _vp, _vp],
     "strix_ep_row_sum": [_vp, _int, _vp, _int, _i64, _i64, _i64, _vp, _vp],
-    "strix_ep_home_sum": [_vp, _vp, _vp, _i64, _i64, _i64, _int, _i64, _i64, _vp, _int, _vp],
+    "strix_ep_home_sum": [_vp, _int, _vp, _vp, _i64, _i64, _i64, _int, _i64, _i64, _vp, _int, _vp],
+    "strix_ep_push_rows": [_vp, _i64, _int, _vp, _vp, _int, _int, _i64, _i64, _vp, _vp, _vp],
+    "strix_ep_row_sum_push": [_vp, _int, _vp, _int, _int, _i64, _i64, _i64, _vp, _int, _vp],
     "strix_hash64": [_vp, _sz],
     "strix_umma_abort_count": [],
     "strix_workspace_refusal_count": [],

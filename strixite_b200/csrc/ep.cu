@@ -201,10 +201,75 @@ __global__ void __launch_bounds__(256) ep_row_sum_kernel(const void *partial, co
     }
 }
 
+// ---- the exchange inside the kernels: peer stores over NVLink instead of a library all-to-all --------------------------------------
+// Every rank holds its receive buffers in memory its peers have mapped (symmetric allocation); `*_ptrs[r]` is rank r's buffer as
+// seen from this GPU. A source writes its block [rank] of the destination's buffer directly, so the transfer is the kernel's own
+// store stream and needs no staging copy; the ranks meet at a barrier (a host-enqueued collective) before anyone reads.
+
+// Token rows and the metadata block to every destination. grid = (C + kMetaBlocks, P): blocks i < C copy row i of destination
+// blockIdx.y (when the plan counted it), the others stream the used part of the metadata block.
+constexpr int kMetaBlocks = 8;
+__global__ void __launch_bounds__(256)
+    ep_push_rows_kernel(const uint4 *x, int row16, const int32_t *rowtok, const int32_t *meta, int rank, int C, int Cs, const uint64_t *rows_ptrs,
+                        const uint64_t *meta_ptrs) {
+    const int r = blockIdx.y, i = blockIdx.x, MW = 4 + 2 * C + 3 * Cs;
+    const int32_t *m = meta + (int64_t)r * MW;
+    if (i < C) {
+        if (i >= m[0]) return;
+        const uint4 *src = x + (int64_t)rowtok[(int64_t)r * C + i] * row16;
+        uint4 *dst = reinterpret_cast<uint4 *>(rows_ptrs[r]) + ((int64_t)rank * C + i) * row16;
+        for (int j = threadIdx.x; j < row16; j += 256) dst[j] = src[j];
+        return;
+    }
+    // metadata: the header and the row table up to n_rows, the slot table up to n_slots (the rest of the block is never read)
+    int32_t *dm = reinterpret_cast<int32_t *>(meta_ptrs[r]) + (int64_t)rank * MW;
+    const int n_head = 4 + 2 * m[0], n_slot_ints = 3 * m[1];
+    const int t = (i - C) * 256 + threadIdx.x, stride = kMetaBlocks * 256;
+    for (int j = t; j < n_head; j += stride) dm[j] = m[j];
+    for (int j = t; j < n_slot_ints; j += stride) dm[4 + 2 * C + j] = m[4 + 2 * C + j];
+}
+
+// Expert side: the row sums of ep_row_sum, each written straight into the home rank's `back` buffer (block [rank] of it), FP32 or
+// F16 (OH: one rounding of the FP32 sum; halves the bytes that cross the links). One block per received row.
+template <bool H, bool OH>
+__global__ void __launch_bounds__(256)
+    ep_row_sum_push_kernel(const void *partial, const int32_t *meta, int rank, int C, int Cs, int d4, const uint64_t *back_ptrs) {
+    const int s = blockIdx.y, i = blockIdx.x;
+    const int32_t *m = meta + (int64_t)s * (4 + 2 * C + 3 * Cs);
+    if (i >= m[0]) return;
+    const int first = m[4 + 2 * i], n = m[4 + 2 * i + 1];
+    const int32_t *sm = m + 4 + 2 * C + 3 * first;
+    const int64_t out_row = ((int64_t)rank * C + i) * d4;
+    for (int j = threadIdx.x; j < d4; j += 256) {
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int q = 0; q < n; ++q) {
+            const float c = __int_as_float(sm[3 * q + 2]);
+            const int64_t e = ((int64_t)s * Cs + first + q) * d4 + j;
+            float4 p;
+            if constexpr (H) {
+                const uint2 u = static_cast<const uint2 *>(partial)[e];
+                const float2 lo = __half22float2(*reinterpret_cast<const __half2 *>(&u.x)), hi = __half22float2(*reinterpret_cast<const __half2 *>(&u.y));
+                p = make_float4(lo.x, lo.y, hi.x, hi.y);
+            } else {
+                p = static_cast<const float4 *>(partial)[e];
+            }
+            v.x = fmaf(c, p.x, v.x), v.y = fmaf(c, p.y, v.y), v.z = fmaf(c, p.z, v.z), v.w = fmaf(c, p.w, v.w);
+        }
+        if constexpr (OH) {
+            const __half2 lo = __floats2half2_rn(v.x, v.y), hi = __floats2half2_rn(v.z, v.w);
+            uint2 u;
+            u.x = *reinterpret_cast<const uint32_t *>(&lo), u.y = *reinterpret_cast<const uint32_t *>(&hi);
+            reinterpret_cast<uint2 *>(back_ptrs[s])[out_row + j] = u;
+        } else {
+            reinterpret_cast<float4 *>(back_ptrs[s])[out_row + j] = v;
+        }
+    }
+}
+
 // Home side: y[t][:] = the rows that came back for token t, added in ascending rank order, rounded once to the activation
 // dtype. A token the router failed (ids -1) or with an invalid id gets a NaN row, as on one device.
-template <typename T>
-__global__ void __launch_bounds__(256) ep_home_sum_kernel(const float4 *back, const int32_t *pos, const int32_t *ids, int A, int E, int P, int C, int d4, T *y) {
+template <typename T, bool BH>  // BH: the returned rows are F16 (ep_row_sum_push with F16 output)
+__global__ void __launch_bounds__(256) ep_home_sum_kernel(const void *back, const int32_t *pos, const int32_t *ids, int A, int E, int P, int C, int d4, T *y) {
     const int t = blockIdx.x;
     bool bad = false;
     for (int a = 0; a < A; ++a) {
@@ -216,7 +281,15 @@ __global__ void __launch_bounds__(256) ep_home_sum_kernel(const float4 *back, co
         for (int r = 0; r < P; ++r) {
             const int p = pos[(int64_t)t * P + r];
             if (p < 0) continue;
-            const float4 b = back[((int64_t)r * C + p) * d4 + j];
+            const int64_t e = ((int64_t)r * C + p) * d4 + j;
+            float4 b;
+            if constexpr (BH) {
+                const uint2 u = static_cast<const uint2 *>(back)[e];
+                const float2 lo = __half22float2(*reinterpret_cast<const __half2 *>(&u.x)), hi = __half22float2(*reinterpret_cast<const __half2 *>(&u.y));
+                b = make_float4(lo.x, lo.y, hi.x, hi.y);
+            } else {
+                b = static_cast<const float4 *>(back)[e];
+            }
             v.x += b.x, v.y += b.y, v.z += b.z, v.w += b.w;
         }
         if (bad) v = make_float4(qnan(), qnan(), qnan(), qnan());
@@ -283,17 +356,51 @@ int strix_ep_row_sum(const void *partial, int partial_f16, const int32_t *meta_r
     return 0;
 }
 
-int strix_ep_home_sum(const float *back, const int32_t *pos, const int32_t *ids, int64_t T, int64_t A, int64_t E, int P, int64_t C, int64_t d, void *y, int act,
-                      void *stream) {
+int strix_ep_home_sum(const void *back, int back_f16, const int32_t *pos, const int32_t *ids, int64_t T, int64_t A, int64_t E, int P, int64_t C, int64_t d, void *y,
+                      int act, void *stream) {
     const char *fn = "ep_home_sum";
     SB_CHECK(back && pos && ids && y, fn, ": null pointer");
     SB_CHECK(P >= 1 && P <= kMaxRanks && T >= 1 && T <= 0x7fffffff && d >= 4 && d % 4 == 0 && act_ok(act) && aligned16(back), fn, ": P = ", P, ", T = ", T, ", d = ", d);
     auto st = static_cast<cudaStream_t>(stream);
-    if (act == kF32)
-        ep_home_sum_kernel<float><<<(unsigned)T, 256, 0, st>>>(reinterpret_cast<const float4 *>(back), pos, ids, (int)A, (int)E, P, (int)C, (int)(d / 4), static_cast<float *>(y));
-    else
-        ep_home_sum_kernel<uint16_t><<<(unsigned)T, 256, 0, st>>>(reinterpret_cast<const float4 *>(back), pos, ids, (int)A, (int)E, P, (int)C, (int)(d / 4),
-                                                                  static_cast<uint16_t *>(y));
+    const int Ai = (int)A, Ei = (int)E, Ci = (int)C, d4 = (int)(d / 4);
+    if (act == kF32) {
+        if (back_f16) ep_home_sum_kernel<float, true><<<(unsigned)T, 256, 0, st>>>(back, pos, ids, Ai, Ei, P, Ci, d4, static_cast<float *>(y));
+        else ep_home_sum_kernel<float, false><<<(unsigned)T, 256, 0, st>>>(back, pos, ids, Ai, Ei, P, Ci, d4, static_cast<float *>(y));
+    } else {
+        if (back_f16) ep_home_sum_kernel<uint16_t, true><<<(unsigned)T, 256, 0, st>>>(back, pos, ids, Ai, Ei, P, Ci, d4, static_cast<uint16_t *>(y));
+        else ep_home_sum_kernel<uint16_t, false><<<(unsigned)T, 256, 0, st>>>(back, pos, ids, Ai, Ei, P, Ci, d4, static_cast<uint16_t *>(y));
+    }
+    SB_LAUNCH_OK(fn);
+    return 0;
+}
+
+int strix_ep_push_rows(const void *x, int64_t d, int act, const int32_t *rowtok, const int32_t *meta, int P, int rank, int64_t C, int64_t Cs, const uint64_t *rows_ptrs,
+                       const uint64_t *meta_ptrs, void *stream) {
+    const char *fn = "ep_push_rows";
+    SB_CHECK(x && rowtok && meta && rows_ptrs && meta_ptrs, fn, ": null pointer");
+    SB_CHECK(act_ok(act) && d >= 8 && (d * act_size(act)) % 16 == 0 && aligned16(x), fn, ": rows of ", d, " ", act_name(act), " values must be whole 16-byte pieces, 16-byte aligned");
+    SB_CHECK(P >= 1 && P <= kMaxRanks && rank >= 0 && rank < P && C >= 1 && C <= 0x7ffffff0 && Cs >= 1, fn, ": P = ", P, ", rank = ", rank, ", C = ", C, ", Cs = ", Cs);
+    ep_push_rows_kernel<<<dim3((unsigned)C + kMetaBlocks, (unsigned)P), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint4 *>(x), (int)(d * act_size(act) / 16), rowtok, meta, rank, (int)C, (int)Cs, rows_ptrs, meta_ptrs);
+    SB_LAUNCH_OK(fn);
+    return 0;
+}
+
+int strix_ep_row_sum_push(const void *partial, int partial_f16, const int32_t *meta_recv, int P, int rank, int64_t C, int64_t Cs, int64_t d, const uint64_t *back_ptrs,
+                          int back_f16, void *stream) {
+    const char *fn = "ep_row_sum_push";
+    SB_CHECK(partial && meta_recv && back_ptrs, fn, ": null pointer");
+    SB_CHECK(P >= 1 && P <= kMaxRanks && rank >= 0 && rank < P && C >= 1 && Cs >= 1 && d >= 4 && d % 4 == 0 && aligned16(partial), fn, ": P = ", P, ", C = ", C, ", d = ", d);
+    const dim3 grid((unsigned)C, (unsigned)P);
+    auto st = static_cast<cudaStream_t>(stream);
+    const int Ci = (int)C, Csi = (int)Cs, d4 = (int)(d / 4);
+    if (partial_f16) {
+        if (back_f16) ep_row_sum_push_kernel<true, true><<<grid, 256, 0, st>>>(partial, meta_recv, rank, Ci, Csi, d4, back_ptrs);
+        else ep_row_sum_push_kernel<true, false><<<grid, 256, 0, st>>>(partial, meta_recv, rank, Ci, Csi, d4, back_ptrs);
+    } else {
+        if (back_f16) ep_row_sum_push_kernel<false, true><<<grid, 256, 0, st>>>(partial, meta_recv, rank, Ci, Csi, d4, back_ptrs);
+        else ep_row_sum_push_kernel<false, false><<<grid, 256, 0, st>>>(partial, meta_recv, rank, Ci, Csi, d4, back_ptrs);
+    }
     SB_LAUNCH_OK(fn);
     return 0;
 }

@@ -133,6 +133,19 @@ class ExpertParallelMoe:
             raise ValueError("ExpertParallelMoe: %d tokens do not split into %d chunks" % (T, n))
         Tc = T // n
         b.begin(x)
+        if getattr(b, "pushes", False):  # the backend's kernels write into the peers' buffers themselves
+            for c in range(n):
+                with b.stream(c):
+                    b.route(c, x[c * Tc:(c + 1) * Tc])
+                    b.plan_push(c)
+            for c in range(n):
+                with b.stream(c):
+                    b.experts_push(c)
+            ys = []
+            for c in range(n):
+                with b.stream(c):
+                    ys.append(b.home(c, b.back(c)))
+            return b.end(ys)
         recv = [None] * n
         for c in range(n):
             with b.stream(c):
@@ -165,7 +178,7 @@ class CudaBackend:
     the shared expert (uniform 4-bit stacks)."""
 
     def __init__(self, d, I, E, k, act, router_w, router_bias, gate_up_local, down_local, world, rank, place, max_local_tokens, chunks=1, math=2,
-                 slot_capacity=None):
+                 slot_capacity=None, peer_group=None):
         from . import kernels as K
         from ._lib import lib
         from .layer import MoeLayer
@@ -205,6 +218,84 @@ class CudaBackend:
                 partial=torch.empty((n_cap, d), dtype=torch.float16, device=dev), summed=z(world, self.Cr, d, dt=torch.float32),
                 back=z(world, self.Cr, d, dt=torch.float32), y=torch.empty((Tc, d), dtype=adt, device=dev)))
         self.launches = 0
+        # peer_group (a process group over the ranks, one GPU each): the receive buffers live in memory every peer has mapped,
+        # and the kernels write their blocks straight into the destination's buffers (push_rows / experts_push) - the exchange
+        # is part of the gather and of the row sum, the ranks only meet at a barrier. Without it: library all-to-alls.
+        self.pushes = False
+        if peer_group is not None and world > 1:
+            try:
+                self._map_peer_buffers(peer_group, adt)
+            except Exception as e:  # noqa: BLE001 - no peer mapping on this system: the all-to-all path serves
+                import sys
+
+                print("strixite_b200.ep: peer-mapped buffers unavailable (%s: %s); using all-to-alls" % (type(e).__name__, e), file=sys.stderr)
+                self.pushes = False
+
+    def _map_peer_buffers(self, group, adt):
+        import os
+
+        import torch.distributed._symmetric_memory as symm
+
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")  # plain peer mappings: the kernels use ordinary stores
+        dev, P = self.dev, self.P
+        self.peer_group = group
+        self.back_dtype = torch.float16  # the sums that travel home: F16, one rounding of each FP32 row sum
+        self._sym = []
+        for b in self.c:
+            tabs = {}
+            for name, shape, dt in (("rows_recv", (P, self.Cr, self.d), adt), ("meta_recv", (P, self.MW), torch.int32),
+                                    ("back", (P, self.Cr, self.d), self.back_dtype)):
+                t = symm.empty(shape, dtype=dt, device=dev)
+                t.zero_()
+                h = symm.rendezvous(t, group)
+                self._sym.append((t, h))
+                b[name] = t
+                tabs[name] = torch.tensor([int(p) for p in h.buffer_ptrs], dtype=torch.int64, device=dev)
+            b["ptrs"] = tabs
+            b["token"] = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.pushes = True
+
+    def _barrier(self, c):
+        """Every rank's kernels enqueued so far on this chunk's stream have finished before any rank's later kernels start: a
+        one-element all-reduce (the library's own bounded, abortable wait - no spin of ours)."""
+        dist.all_reduce(self.c[c]["token"], group=self.peer_group)
+
+    def use_peer_tables(self, tables, back_dtype=torch.float16):
+        """Installs the address tables of the peers' receive buffers for every chunk: tables[c][name] = int64 device tensor of P
+        addresses for name in rows_recv / meta_recv / back (how _map_peer_buffers sets them; tests with every rank on one GPU
+        build them by hand)."""
+        self.back_dtype = back_dtype
+        for b, t in zip(self.c, tables):
+            b["ptrs"] = t
+        self.pushes = True
+
+    def plan_push(self, c, barrier=True):
+        """plan(), with the rows and the metadata written into the destinations' receive buffers by the gather itself."""
+        from ._lib import call
+
+        K, b = self.K, self.c[c]
+        T = b["x"].shape[0]
+        call("strix_ep_plan", K._p(b["ids"]), K._p(b["coef"]), T, self.A, self.E, K._p(self.owner), K._p(self.local_of), self.P, self.rank, self.Cr, self.Cs,
+             K._p(b["rowtok"]), K._p(b["meta_send"]), K._p(b["pos"]), K._p(b["flags"]), K._p(b["plan_scratch"]), self._sp(c))
+        call("strix_ep_push_rows", K._p(b["x"]), self.d, int(self.act), K._p(b["rowtok"]), K._p(b["meta_send"]), self.P, self.rank, self.Cr, self.Cs,
+             K._p(b["ptrs"]["rows_recv"]), K._p(b["ptrs"]["meta_recv"]), self._sp(c))
+        self.launches += 4
+        if barrier:
+            self._barrier(c)
+
+    def experts_push(self, c, barrier=True):
+        """experts(), with every row sum written into its home rank's `back` buffer by the summing kernel itself."""
+        from ._lib import call
+
+        K, b = self.K, self.c[c]
+        b["meta_last"] = b["meta_recv"]
+        call("strix_ep_unpack", K._p(b["meta_recv"]), self.P, self.Cr, self.Cs, K._p(b["slot_ids"]), K._p(b["slot_row"]), self._sp(c))
+        b["shard"].experts_partial(b["rows_recv"].reshape(-1, self.d), b["slot_ids"], partial=b["partial"], stream=self.streams[c], row_index=b["slot_row"])
+        call("strix_ep_row_sum_push", K._p(b["partial"]), 1 if b["partial"].dtype == torch.float16 else 0, K._p(b["meta_recv"]), self.P, self.rank, self.Cr, self.Cs,
+             self.d, K._p(b["ptrs"]["back"]), 1 if self.back_dtype == torch.float16 else 0, self._sp(c))
+        self.launches += 9
+        if barrier:
+            self._barrier(c)
 
     # ---- the driver's hooks -------------------------------------------------------------------------------------------------
     def stream(self, c):
@@ -277,7 +368,7 @@ class CudaBackend:
 
         K, b = self.K, self.c[c]
         T = b["x"].shape[0]
-        call("strix_ep_home_sum", K._p(back), K._p(b["pos"]), K._p(b["ids"]), T, self.A, self.E, self.P, self.Cr, self.d, K._p(b["y"][:T]), int(self.act), self._sp(c))
+        call("strix_ep_home_sum", K._p(back), 1 if back.dtype == torch.float16 else 0, K._p(b["pos"]), K._p(b["ids"]), T, self.A, self.E, self.P, self.Cr, self.d, K._p(b["y"][:T]), int(self.act), self._sp(c))
         self.launches += 1
         return b["y"][:T]
 
@@ -327,16 +418,20 @@ class CudaLayer:
 
 
 def cuda_layer(d, I, E, k, act, router_w, router_bias, gate_up_local, down_local, world, rank, max_local_tokens, placement=None, group=None, math=2, chunks=0,
-               dedup=True, slot_capacity=None):
+               dedup=True, slot_capacity=None, peer_stores=True):
     """The expert-parallel layer on this rank's GPU (see CudaBackend). placement: the dict of placement() (default: contiguous).
-    chunks: token chunks per step on separate streams (0 = two when several ranks exchange, else one)."""
+    chunks: token chunks per step on separate streams (0 = one). peer_stores: with several ranks, keep the receive buffers in
+    peer-mapped memory and let the gather and the row-sum kernels write into the destinations' buffers (False: all-to-alls)."""
     if not dedup:
         raise ValueError("cuda_layer: the one-row-per-slot exchange was removed; rows go once per (token, rank)")
     place = placement if placement is not None else globals()["placement"](E, world, balanced=False)
     if chunks <= 0:
-        chunks = 2 if world > 1 and max_local_tokens % 2 == 0 else 1
+        chunks = 1
+    peer_group = None
+    if peer_stores and world > 1:  # peer-mapped receive buffers: the exchange rides on the kernels' own stores
+        peer_group = group if group is not None else dist.group.WORLD
     be = CudaBackend(d, I, E, k, act, router_w, router_bias, gate_up_local, down_local, world, rank, place, max_local_tokens, chunks=chunks, math=math,
-                     slot_capacity=slot_capacity)
+                     slot_capacity=slot_capacity, peer_group=peer_group)
     return CudaLayer(be, world, rank, group=group)
 
 

@@ -33,7 +33,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _backend(L, world, rank, place, Tl, chunks=1, device="cuda"):
+def _backend(L, world, rank, place, Tl, chunks=1, device="cuda", peer_group=None):
     from strixite_b200 import ep as EP
     from strixite_b200 import kernels as K
 
@@ -41,7 +41,7 @@ def _backend(L, world, rank, place, Tl, chunks=1, device="cuda"):
     bias = torch.from_numpy(L["router_bias"]).to(device)
     gu, dn = upload_stack(L["gate_up"]), upload_stack(L["down"])
     return EP.CudaBackend(D, I, E, K_TOP, K.Act.BF16, rw, bias, EP.shard_stack(gu, E, world, rank, place), EP.shard_stack(dn, E, world, rank, place), world,
-                          rank, place, Tl, chunks=chunks)
+                          rank, place, Tl, chunks=chunks, peer_group=peer_group)
 
 
 @pytest.mark.parametrize("P,rank", [(1, 0), (2, 1), (4, 2), (8, 5)])
@@ -130,6 +130,29 @@ def test_one_rank_is_the_single_device_layer_bit_for_bit():
         assert layer.launches_per_step() > 0 and layer.received_slots() == T * (K_TOP + 1)
 
 
+def _emulate_push(P, balanced, L, x):
+    """The same with the kernels writing into the "peers'" receive buffers themselves (strix_ep_push_rows,
+    strix_ep_row_sum_push): every rank's buffers are on this GPU, so the address tables simply point at them."""
+    from strixite_b200 import ep as EP
+
+    Tl = T // P
+    place = EP.placement(E, P, L["router_bias"], K_TOP, balanced=balanced)
+    bes = [_backend(L, P, r, place, Tl) for r in range(P)]
+    for be in bes:
+        be.c[0]["back"] = torch.zeros((P, be.Cr, D), dtype=torch.float16, device="cuda")
+    table = {n: torch.tensor([be.c[0][n].data_ptr() for be in bes], dtype=torch.int64, device="cuda") for n in ("rows_recv", "meta_recv", "back")}
+    xs = [to_torch_act(x[r * Tl:(r + 1) * Tl].copy()) for r in range(P)]
+    for r, be in enumerate(bes):
+        be.use_peer_tables([table])
+        be.begin(xs[r])
+        be.route(0, xs[r])
+        be.plan_push(0, barrier=False)
+    for be in bes:
+        be.experts_push(0, barrier=False)
+    ys = [to_np_act(be.home(0, be.c[0]["back"])) for be in bes]
+    return ys, bes
+
+
 def _emulate(P, balanced, L, x):
     """Every rank's backend lives on this GPU; the all-to-all is done by hand (block [s -> r] of rank s's send buffer becomes
     block s of rank r's receive buffer). The kernels, capacities and tables are exactly the multi-rank ones."""
@@ -173,6 +196,24 @@ def test_several_ranks_emulated_on_one_gpu(P, balanced):
     assert sum(be.received_slots() for be in bes) == Tl * P * (K_TOP + 1)
 
 
+@pytest.mark.parametrize("P,balanced", [(2, True), (4, False), (8, True)])
+def test_peer_store_exchange_emulated_on_one_gpu(P, balanced):
+    L, x = _layer(), _tokens()
+    Tl = T // P
+    ys, bes = _emulate_push(P, balanced, L, x)
+    for be in bes:
+        be.check()
+    y = np.concatenate(ys)
+    base, _ = _emulate(P, balanced, L, x)
+    want = _single_device(L, x[: Tl * P])
+    # against the all-to-all form: the returned sums are F16 here - one more rounding of 2^-11 before the BF16 output's 2^-8
+    # moves about one output in sixteen to the neighbouring BF16 value, never further
+    assert (y != np.concatenate(base)).mean() < 0.15
+    assert rel_err_rows(oracle.to_f32(y), oracle.to_f32(np.concatenate(base))) < 2.0 ** -7
+    assert rel_err_rows(oracle.to_f32(y), oracle.to_f32(want)) < 2.0 ** -7
+    assert sum(be.received_slots() for be in bes) == Tl * P * (K_TOP + 1)
+
+
 def test_a_token_with_a_non_finite_logit_poisons_only_itself():
     """strixite kernels/moe_router.hpp: a token whose logits are not finite gets ids -1 and a NaN output row; every other
     token of every rank is untouched, and the home rank's error word names it."""
@@ -193,7 +234,7 @@ def test_a_token_with_a_non_finite_logit_poisons_only_itself():
     bes[1].check()
 
 
-def _run_rank(rank, world, port, out_dir, chunks):
+def _run_rank(rank, world, port, out_dir, chunks, peer):
     from strixite_b200 import ep as EP
     from strixite_b200 import kernels as K
 
@@ -205,7 +246,8 @@ def _run_rank(rank, world, port, out_dir, chunks):
         L, x = _layer(), _tokens()
         Tl = T // world
         place = EP.placement(E, world, L["router_bias"], K_TOP, balanced=True)
-        be = _backend(L, world, rank, place, Tl, chunks=chunks, device="cuda:%d" % rank)
+        be = _backend(L, world, rank, place, Tl, chunks=chunks, device="cuda:%d" % rank, peer_group=dist.group.WORLD if peer else None)
+        assert be.pushes == peer
         layer = EP.CudaLayer(be, world, rank)
         xr = to_torch_act(x[rank * Tl:(rank + 1) * Tl].copy(), device="cuda:%d" % rank)
         y = layer.forward(xr)
@@ -218,10 +260,11 @@ def _run_rank(rank, world, port, out_dir, chunks):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("chunks", (1, 2))
+@pytest.mark.parametrize("chunks,peer", [(1, False), (2, False), (1, True), (2, True)])
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_two_ranks_over_nccl(tmp_path, chunks):
-    mp.spawn(_run_rank, args=(2, _free_port(), str(tmp_path), chunks), nprocs=2, join=True)
+def test_two_ranks_over_nccl(tmp_path, chunks, peer):
+    """Two processes, a GPU each: the all-to-all exchange and (peer) the exchange by the kernels' own peer stores."""
+    mp.spawn(_run_rank, args=(2, _free_port(), str(tmp_path), chunks, peer), nprocs=2, join=True)
     y = np.concatenate([np.load(tmp_path / ("y%d.npy" % r)) for r in range(2)])
     L, x = _layer(), _tokens()
     want = _single_device(L, x)

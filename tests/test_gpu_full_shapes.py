@@ -54,7 +54,7 @@ def test_prefill_4096_tokens_fp32_activations():
 
 def test_expert_parallel_batch_of_16384_tokens_on_one_rank():
     cfg = dict(bench.WORKLOADS["ep_prefill16384"])
-    args = types.SimpleNamespace(ep_contiguous=False, ep_chunks=0)
+    args = types.SimpleNamespace(ep_contiguous=False, ep_chunks=0, ep_all_to_all=False)
     out, _ = bench.run_ep(args, cfg, steps=2, warmup=3, rank=0, world=1, local=0, device="cuda:0", P=bench.peaks(), line={}, want_parity=True)
     p = out["parity"]
     assert p["ids_equal"] and p["ids_rows_checked"] == 16384 and p["finite"]
