@@ -55,11 +55,11 @@ BF16_STEP = 2.0 ** -9  # half a BF16 step relative to the element: what rounding
 # DRAM bytes (read + write) of the dominant kernel per launch, from ncu captures of small rings of the same workloads; the
 # summaries with the full commands are in profiles/. Constants from a profile, not measured in this run.
 TRAFFIC = {
-    "decode1": dict(bytes=None, kernel="decode_stream_kernel", source="profiles/decode_stream_kernel_decode1_verify6.md"),
-    "verify6": dict(bytes=None, kernel="decode_stream_kernel", source="profiles/decode_stream_kernel_decode1_verify6.md"),
-    "stack4": dict(bytes=None, kernel="decode_stream_kernel", source="profiles/decode_stream_kernel_stack4.md"),
-    "prefill4096": dict(bytes=None, kernel="ffn_umma_kernel<0>", source="profiles/ffn_umma_kernel_prefill4096.md"),
-    "ep_prefill16384": dict(bytes=None, kernel="ffn_umma_kernel<0>", source="profiles/ffn_umma_kernel_prefill4096.md"),
+    "decode1": dict(bytes=22.68e6, kernel="decode_stream_kernel", source="profiles/decode_stream_kernel_decode1_verify6.md"),
+    "verify6": dict(bytes=101.13e6, kernel="decode_stream_kernel", source="profiles/decode_stream_kernel_decode1_verify6.md"),
+    "stack4": dict(bytes=479.15e6, kernel="decode_stream_kernel (one launch = one of the 4 layers)", source="profiles/decode_stream_kernel_stack4.md"),
+    "prefill4096": dict(bytes=779.07e6, kernel="ffn_umma_kernel<0, 128, 0>", source="profiles/ffn_umma_kernel_prefill4096.md"),
+    "ep_prefill16384": dict(bytes=1144.18e6, kernel="ffn_umma_kernel<0, 128, 2> (one GPU, 16384 tokens)", source="profiles/ffn_umma_kernel_ep_prefill16384.md"),
 }
 
 
@@ -468,16 +468,18 @@ def measure_single(name, cfg, steps, warmup, rank, world, local, device, P, dist
             per_step_bytes.append(tot)
         step_s = ms * 1e-3 / steps
         tr = TRAFFIC.get(name, {})
-        traffic = None if tr.get("bytes") is None else dict(dram_bytes_per_launch=tr["bytes"], kernel=tr["kernel"], source=tr["source"] + " (ncu capture of a small ring; a constant, not measured in this run)")
+        traffic = tr.get("bytes")
+        traffic_note = None if traffic is None else dict(unit="bytes per launch (dram read + write)", kernel=tr["kernel"],
+                                                          source=tr["source"] + " (ncu capture of a small ring of this workload; a constant, not measured in this run)")
         if cfg["M"] <= 64:
             ach = float(np.mean(per_step_bytes)) / step_s / 1e9
-            out["roofline"] = dict(bound="hbm", achieved=ach, peak=P["hbm"], unit="GB/s", frac=ach / P["hbm"], traffic=traffic, peak_source=P["source"],
+            out["roofline"] = dict(bound="hbm", achieved=ach, peak=P["hbm"], unit="GB/s", frac=ach / P["hbm"], traffic=traffic, traffic_note=traffic_note, peak_source=P["source"],
                                    frac_of_nominal_8TBs=ach / 8000.0, algorithmic_bytes_per_step=float(np.mean(per_step_bytes)),
                                    distinct_experts_per_layer=float(np.mean(distinct)), kernel="whole step (all launches of one pass over the layer(s))")
         else:
             fl = flops_of(cfg, l0.A)
             ach = fl / step_s / 1e12
-            out["roofline"] = dict(bound="tensor", achieved=ach, peak=P["tensor"], unit="TFLOP/s", frac=ach / P["tensor"], traffic=traffic,
+            out["roofline"] = dict(bound="tensor", achieved=ach, peak=P["tensor"], unit="TFLOP/s", frac=ach / P["tensor"], traffic=traffic, traffic_note=traffic_note,
                                    peak_source=P["source"], algorithmic_flops_per_step=fl, kernel="whole step")
         per_ring = kernel_nodes(full)
         if per_ring is None:
@@ -717,7 +719,10 @@ def run_ep(args, cfg, steps, warmup, rank, world, local, device, P, line, want_p
     ach = fl / step_s / 1e12
     tr = TRAFFIC["ep_prefill16384"]
     out["roofline"] = dict(bound="tensor", achieved=ach, peak=P["tensor"] * world, unit="TFLOP/s", frac=ach / (P["tensor"] * world),
-                           traffic=None if tr["bytes"] is None else dict(dram_bytes_per_launch=tr["bytes"], kernel=tr["kernel"], source=tr["source"]),
+                           traffic=None if tr["bytes"] is None else tr["bytes"] / world,
+                           traffic_note=dict(unit="bytes per launch and rank (dram read + write)", kernel=tr["kernel"],
+                                             source=tr["source"] + (" (ncu capture on one GPU; a constant, not measured in this run" +
+                                                                    ("; scaled by 1 / ranks: a rank streams its share of the experts and of the slots)" if world > 1 else ")"))),
                            peak_source=P["source"], algorithmic_flops_per_step=fl, kernel="whole step, all ranks",
                            load_imbalance_max_over_mean_slots=float(mx[1].item() / max(sm[1].item() / world, 1.0)))
     out["load_imbalance"] = out["roofline"]["load_imbalance_max_over_mean_slots"]

@@ -184,11 +184,17 @@ __global__ void __launch_bounds__(kRouteThreads)
     }
     int count = 0;
     if (t < B) {
-#pragma unroll 8
-        for (int g = 0; g < kSegs; ++g) {
-            const int c = scratch[g * B + t];
-            scratch[g * B + t] = count;  // this segment's first rank inside the bucket
-            count += c;
+        // sixteen counts in flight per round trip (a load after a store to the same array would otherwise wait for it)
+        static_assert(kSegs % 16 == 0, "the bucket's column is read in batches of 16");
+        for (int g0 = 0; g0 < kSegs; g0 += 16) {
+            int c[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) c[j] = scratch[(g0 + j) * B + t];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                scratch[(g0 + j) * B + t] = count;  // this segment's first rank inside the bucket
+                count += c[j];
+            }
         }
     }
     const int st = block_exclusive_scan(count, warp_tot, &total_a);
@@ -222,14 +228,14 @@ __global__ void __launch_bounds__(kSegWarps * 32) route_place_kernel(const int32
     for (int i = lane; i < B; i += 32) pos[i] = offsets[i] + scratch[g * B + i];
     __syncwarp();
     const int seg = seg_len(S), s_begin = min(S, g * seg), s_end = min(S, s_begin + seg);
+    int32_t next_id = s_begin + lane < s_end ? ids[s_begin + lane] : 0;  // the next step's id is loaded under this step's work
     for (int s0 = s_begin; s0 < s_end; s0 += 32) {
         const int s = s0 + lane;
         const bool live = s < s_end;
+        const int32_t id = next_id;
+        if (s + 32 < s_end) next_id = ids[s + 32];
         int b = 0x40000000 | lane;  // idle lanes: a bucket of their own
-        if (live) {
-            const int32_t id = ids[s];
-            b = (id < 0 || id >= E) ? E : id;
-        }
+        if (live) b = (id < 0 || id >= E) ? E : id;
         const unsigned same = __match_any_sync(0xffffffffu, b);
         const int rank = __popc(same & ((1u << lane) - 1u));
         if (live) slots[pos[b] + rank] = s;

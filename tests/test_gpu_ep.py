@@ -268,5 +268,6 @@ def test_two_ranks_over_nccl(tmp_path, chunks, peer):
     y = np.concatenate([np.load(tmp_path / ("y%d.npy" % r)) for r in range(2)])
     L, x = _layer(), _tokens()
     want = _single_device(L, x)
-    assert (y != want).mean() < 0.02
+    # FP32 sums back: another association of the same sum; F16 sums back (peer): one more rounding before the BF16 output
+    assert (y != want).mean() < (0.15 if peer else 0.02)
     assert rel_err_rows(oracle.to_f32(y), oracle.to_f32(want)) < 2.0 ** -7
