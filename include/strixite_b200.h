@@ -221,7 +221,9 @@ int strix_linear_q5_experts_combine_grouped(const void *h, const strix_qview *w,
  *     current) and caches it; make that first call outside any stream capture.
  *   - Every call on a device uses the same array. Nothing in it has to be zero beforehand (each partial sum that is
  *     read is written first by the same call), but two calls whose kernels can overlap in time - different streams,
- *     or different host threads without ordering - race on it; calls on one stream are safe. */
+ *     or different host threads without ordering - race on it; calls on one stream are safe. The array's address is looked up
+ * once per device and cached: after cudaDeviceReset() the cached address is stale - do not call this entry again in a process
+ * that reset the device. */
 #define STRIX_FIXED_PARTIAL_FLOATS (1 << 20)
 int strix_linear_q4_experts_combine_grouped_fixed(const void *h, const strix_qview *w, int64_t E, const int32_t *ids,
                                                   const float *coef, const void *ws, size_t ws_bytes, int64_t M,
