@@ -14,7 +14,8 @@ import subprocess
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-DEFAULT_REF = os.environ.get("STRIXITE_REFERENCE", "/root/reference")
+# The strixite source tree: STRIXITE_REFERENCE, or a checkout named "reference" beside this repository.
+DEFAULT_REF = os.environ.get("STRIXITE_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
 
 
 def _run(cmd):

@@ -1,7 +1,7 @@
 """CPU: the reference-side shim (include/strix_kernels_shim.cpp: strixite's kernel functions defined over the C ABI) must compile
 against the reference's own headers - every forwarded declaration matched in name, argument types and order. Needs the
-reference tree (STRIXITE_REFERENCE, default /root/reference); skipped where it is absent. <hip/hip_runtime.h> is a stand-in
-(tests/stubs) since the check is syntax only."""
+reference tree (STRIXITE_REFERENCE, default: a checkout named "reference" beside this repository); skipped where it is
+absent. <hip/hip_runtime.h> is a stand-in (tests/stubs) since the check is syntax only."""
 import os
 import re
 import shutil
@@ -10,7 +10,7 @@ import subprocess
 import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-REF = os.environ.get("STRIXITE_REFERENCE", "/root/reference")
+REF = os.environ.get("STRIXITE_REFERENCE") or os.path.join(os.path.dirname(ROOT), "reference")
 SHIM = os.path.join(ROOT, "include", "strix_kernels_shim.cpp")
 
 
