@@ -9,13 +9,14 @@
 //   hc_mix_up    h [T, r], W_up [H d, r] (Q4 or Q8, CHUNK-major: 32-code chunk c of row n at q[(c N + n) * chunk bytes],
 //                group g's scale / min at [g N + n]; strixite formats/q4.hpp:41-55): per row (s, j)
 //                z = sigmoid(W_up[s d + j] . h), u[j] = (1 / H) sum_s z * X[s d + j] * inv_s * (1 + norm_w[s d + j]).
-// Both are small weight-streaming kernels (a 324 x 10240 Q4 matrix is 1.9 MB): a warp per weight row (down) or a lane per
-// weight row with the chunk-major layout making a warp's loads one contiguous run (up).
+// Both are small weight-streaming kernels (a 324 x 10240 Q4 matrix is 1.9 MB): a block per weight row with a warp per stream
+// (down), or a lane per weight row with the chunk-major layout making a warp's loads one contiguous run (up).
 #include "common.cuh"
 
 #include "strixite_b200.h"
 
 #include <cmath>
+#include <type_traits>
 #include <cstring>
 
 namespace {
@@ -25,37 +26,56 @@ using namespace sb;
 constexpr int kH = 4;          // streams
 constexpr int kMaxR = 1024;    // low rank, kept in shared memory by hc_mix_up
 
-// ---- hc_mix_down: one warp per weight row, all of K; grid.y = token ---------------------------------------------------------
-template <typename T, int BITS>
-__global__ void __launch_bounds__(256) hc_down_kernel(const T *x, strix_qview w, int64_t d, int r, float eps, float *h, float *w_in, float *inv) {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int64_t n = (int64_t)blockIdx.x * 8 + warp, t = blockIdx.y, K = w.K;
-    if (n >= w.N) return;
-    const T *xr = x + t * K;
+// ---- hc_mix_down: one block per weight row and batch of up to kDownTokens tokens, a warp per stream (its quarter of K). The
+//      row's codes are decoded once per chunk and applied to every token of the batch; a token's arithmetic does not depend on
+//      the batch it is in. A handful of tokens (decode, verify) run one token per block: these launches are latency-bound, and
+//      more blocks beat fewer decodes (T = 5: 10 us either way for down, 8 vs 14 us for up); from kBatchFrom tokens on the
+//      batches win (T = 64: 88 -> 71 us down, 53 -> 34 us up). --------------------------------------------------------------------
+constexpr int kBatchFrom = 16, kDownBatch = 8, kUpBatch = 4;
+template <typename T, int BITS, int kDownTokens>
+__global__ void __launch_bounds__(32 * kH)
+    hc_down_kernel(const T *x, strix_qview w, int64_t Tn, int64_t d, int r, float eps, float *h, float *w_in, float *inv) {
+    __shared__ float ps[kDownTokens][kH], sqs[kDownTokens][kH];
+    const int lane = threadIdx.x & 31, s = threadIdx.x >> 5;  // s: the stream this warp covers
+    const int64_t n = blockIdx.x, t0 = (int64_t)blockIdx.y * kDownTokens, K = w.K;
+    const int nt = (int)(Tn - t0 < kDownTokens ? Tn - t0 : kDownTokens);
     const uint8_t *row = w.q + n * row_bytes(BITS, K);
     const uint16_t *srow = w.scale + n * (K / w.G), *mrow = w.minv + n * (K / w.G);
-    float p[kH] = {0.f, 0.f, 0.f, 0.f}, sq[kH] = {0.f, 0.f, 0.f, 0.f};
-    for (int64_t c = lane; c < K / 32; c += 32) {
-        float xv[32], code[32];
-        load_x32(xr, c * 32, xv);
+    float p[kDownTokens], sq[kDownTokens];
+#pragma unroll
+    for (int tt = 0; tt < kDownTokens; ++tt) p[tt] = 0.f, sq[tt] = 0.f;
+    const int64_t c0 = (int64_t)s * (d / 32), c1 = c0 + d / 32;  // a 32-code chunk lies inside one stream: d % 32 == 0
+    for (int64_t c = c0 + lane; c < c1; c += 32) {
+        float code[32];
         load_codes32<BITS>(row, K, c, code);
-        float dot = 0.f, xsum = 0.f, s2 = 0.f;
+        const float sc = bf16_bits_to_f32(srow[c * 32 / w.G]), mn = bf16_bits_to_f32(mrow[c * 32 / w.G]);
 #pragma unroll
-        for (int i = 0; i < 32; ++i) dot = fmaf(xv[i], code[i], dot), xsum += xv[i], s2 = fmaf(xv[i], xv[i], s2);
-        const float pv = fmaf(bf16_bits_to_f32(srow[c * 32 / w.G]), dot, bf16_bits_to_f32(mrow[c * 32 / w.G]) * xsum);
-        const int s = (int)(c * 32 / d);  // a 32-code chunk lies inside one stream: d % 32 == 0
+        for (int tt = 0; tt < kDownTokens; ++tt) {
+            if (tt >= nt) break;
+            float xv[32];
+            load_x32(x + (t0 + tt) * K, c * 32, xv);
+            float dot = 0.f, xsum = 0.f, s2 = sq[tt];
 #pragma unroll
-        for (int q = 0; q < kH; ++q)
-            if (q == s) p[q] += pv, sq[q] += s2;
+            for (int i = 0; i < 32; ++i) dot = fmaf(xv[i], code[i], dot), xsum += xv[i], s2 = fmaf(xv[i], xv[i], s2);
+            sq[tt] = s2;
+            p[tt] += fmaf(sc, dot, mn * xsum);
+        }
     }
 #pragma unroll
-    for (int q = 0; q < kH; ++q) p[q] = warp_sum(p[q]), sq[q] = warp_sum(sq[q]);
-    if (lane != 0) return;
+    for (int tt = 0; tt < kDownTokens; ++tt) {
+        if (tt >= nt) break;
+        const float pv = warp_sum(p[tt]), sv = warp_sum(sq[tt]);
+        if (lane == 0) ps[tt][s] = pv, sqs[tt][s] = sv;
+    }
+    __syncthreads();
+    const int tt = threadIdx.x;  // thread tt finishes token tt of the batch
+    if (tt >= nt) return;
+    const int64_t t = t0 + tt;
     float a = 0.f, iv[kH];
 #pragma unroll
     for (int q = 0; q < kH; ++q) {
-        iv[q] = 1.0f / sqrtf(sq[q] / (float)d + eps);
-        a = fmaf(iv[q], p[q], a);
+        iv[q] = 1.0f / sqrtf(sqs[tt][q] / (float)d + eps);
+        a = fmaf(iv[q], ps[tt][q], a);
     }
     const float z = a / (float)kH;
     if (n < r) h[t * r + n] = z / (1.0f + expf(-z));
@@ -83,41 +103,60 @@ __device__ __forceinline__ void load_chunk_cm(const uint8_t *q, int64_t N, int64
     }
 }
 
-template <typename T, int BITS>
-__global__ void __launch_bounds__(128) hc_up_kernel(const float *h, strix_qview w, const T *x, const float *norm_w, const float *inv, int64_t d, T *u) {
-    __shared__ float hs[kMaxR], hsum[kMaxR / 32], contrib[kH][32];
+// A block also takes up to kUpTokens tokens: a weight chunk is decoded once and dotted with every token's h.
+template <typename T, int BITS, int kUpTokens>
+__global__ void __launch_bounds__(128)
+    hc_up_kernel(const float *h, strix_qview w, const T *x, const float *norm_w, const float *inv, int64_t Tn, int64_t d, T *u) {
+    __shared__ float hs[kUpTokens][kMaxR], hsum[kUpTokens][kMaxR / 32], contrib[kUpTokens][kH][32];
     const int lane = threadIdx.x & 31, s = threadIdx.x >> 5, r = (int)w.K;
-    const int64_t t = blockIdx.y, j = (int64_t)blockIdx.x * 32 + lane, N = w.N;
-    for (int i = threadIdx.x; i < r; i += 128) hs[i] = h[t * r + i];
+    const int64_t t0 = (int64_t)blockIdx.y * kUpTokens, j = (int64_t)blockIdx.x * 32 + lane, N = w.N;
+    const int nt = (int)(Tn - t0 < kUpTokens ? Tn - t0 : kUpTokens);
+    for (int tt = 0; tt < nt; ++tt)
+        for (int i = threadIdx.x; i < r; i += 128) hs[tt][i] = h[(t0 + tt) * r + i];
     __syncthreads();
-    for (int c = threadIdx.x; c < r / 32; c += 128) {
+    for (int i = threadIdx.x; i < nt * (r / 32); i += 128) {
+        const int tt = i / (r / 32), c = i % (r / 32);
         float a = 0.f;
-        for (int k = 0; k < 32; ++k) a += hs[c * 32 + k];
-        hsum[c] = a;
+        for (int k = 0; k < 32; ++k) a += hs[tt][c * 32 + k];
+        hsum[tt][c] = a;
     }
     __syncthreads();
     if (j < d) {
         const int64_t row = (int64_t)s * d + j;
-        float acc = 0.f;
+        float acc[kUpTokens];
+#pragma unroll
+        for (int tt = 0; tt < kUpTokens; ++tt) acc[tt] = 0.f;
         for (int c = 0; c < r / 32; ++c) {
             float code[32];
             load_chunk_cm<BITS>(w.q, N, row, c, code);
             const int64_t gi = (int64_t)(c * 32 / w.G) * N + row;
-            float dot = 0.f;
+            const float sc = bf16_bits_to_f32(__ldg(w.scale + gi)), mn = bf16_bits_to_f32(__ldg(w.minv + gi));
 #pragma unroll
-            for (int i = 0; i < 32; ++i) dot = fmaf(hs[c * 32 + i], code[i], dot);
-            acc = fmaf(bf16_bits_to_f32(__ldg(w.scale + gi)), dot, fmaf(bf16_bits_to_f32(__ldg(w.minv + gi)), hsum[c], acc));
+            for (int tt = 0; tt < kUpTokens; ++tt) {
+                if (tt >= nt) break;
+                float dot = 0.f;
+#pragma unroll
+                for (int i = 0; i < 32; ++i) dot = fmaf(hs[tt][c * 32 + i], code[i], dot);
+                acc[tt] = fmaf(sc, dot, fmaf(mn, hsum[tt][c], acc[tt]));
+            }
         }
-        const float z = 1.0f / (1.0f + expf(-acc));
-        contrib[s][lane] = z * (ld_act(x, t * N + row) * inv[t * kH + s] * (1.0f + norm_w[row]));
+        const float nw = 1.0f + norm_w[row];
+#pragma unroll
+        for (int tt = 0; tt < kUpTokens; ++tt) {
+            if (tt >= nt) break;
+            const int64_t t = t0 + tt;
+            const float z = 1.0f / (1.0f + expf(-acc[tt]));
+            contrib[tt][s][lane] = z * (ld_act(x, t * N + row) * inv[t * kH + s] * nw);
+        }
     }
     __syncthreads();
-    if (s == 0 && j < d) {
-        float sum = 0.f;
+    if (s == 0 && j < d)
+        for (int tt = 0; tt < nt; ++tt) {
+            float sum = 0.f;
 #pragma unroll
-        for (int q = 0; q < kH; ++q) sum += contrib[q][lane];
-        st_act(u, t * d + j, sum / (float)kH);
-    }
+            for (int q = 0; q < kH; ++q) sum += contrib[tt][q][lane];
+            st_act(u, (t0 + tt) * d + j, sum / (float)kH);
+        }
 }
 
 // ---- hc_inject_inv: the injection and the next mix's inverse RMS of the updated streams in one pass; block = token -----------------
@@ -173,15 +212,23 @@ int strix_hc_mix_down(const void *x, const strix_qview *w, int bits, int64_t T, 
     SB_CHECK(w->K == H * d && w->N == R, fn, ": weight [", w->N, ", ", w->K, "], expected [", R, ", ", H * d, "]");
     SB_CHECK(aligned16(x) && act_ok(act), fn, ": x ", x, " must be 16-byte aligned; activation dtype ", act);
     SB_CHECK(std::isfinite(eps) && eps > 0.f, fn, ": eps must be finite and > 0, got ", eps);
-    const dim3 grid((unsigned)((R + 7) / 8), (unsigned)T);
     auto st = static_cast<cudaStream_t>(stream);
-    if (act == kF32) {
-        if (bits == 4) hc_down_kernel<float, 4><<<grid, 256, 0, st>>>((const float *)x, *w, d, (int)r, eps, h, w_in, inv);
-        else hc_down_kernel<float, 8><<<grid, 256, 0, st>>>((const float *)x, *w, d, (int)r, eps, h, w_in, inv);
-    } else {
-        if (bits == 4) hc_down_kernel<uint16_t, 4><<<grid, 256, 0, st>>>((const uint16_t *)x, *w, d, (int)r, eps, h, w_in, inv);
-        else hc_down_kernel<uint16_t, 8><<<grid, 256, 0, st>>>((const uint16_t *)x, *w, d, (int)r, eps, h, w_in, inv);
-    }
+    auto launch = [&](auto tag, auto bits_tag, auto mt_tag) {
+        using X = decltype(tag);
+        constexpr int B = decltype(bits_tag)::value, MT = decltype(mt_tag)::value;
+        const dim3 grid((unsigned)R, (unsigned)((T + MT - 1) / MT));
+        hc_down_kernel<X, B, MT><<<grid, 32 * kH, 0, st>>>((const X *)x, *w, T, d, (int)r, eps, h, w_in, inv);
+    };
+    auto by_batch = [&](auto tag, auto bits_tag) {
+        if (T < kBatchFrom) launch(tag, bits_tag, std::integral_constant<int, 1>{});
+        else launch(tag, bits_tag, std::integral_constant<int, kDownBatch>{});
+    };
+    auto by_bits = [&](auto tag) {
+        if (bits == 4) by_batch(tag, std::integral_constant<int, 4>{});
+        else by_batch(tag, std::integral_constant<int, 8>{});
+    };
+    if (act == kF32) by_bits(float{});
+    else by_bits(uint16_t{});
     SB_LAUNCH_OK(fn, " T=", T, " d=", d, " r=", r);
     return 0;
 }
@@ -195,15 +242,23 @@ int strix_hc_mix_up(const float *h, const strix_qview *w_up, int bits, const voi
     SB_CHECK(T >= 1 && T <= 65535 && d >= 1 && w_up->N == H * d, fn, ": T = ", T, ", W_up has ", w_up->N, " rows, expected H*d = ", H * d);
     SB_CHECK(w_up->K >= 32 && w_up->K <= kMaxR, fn, ": r = ", w_up->K, ", expected 32..", kMaxR, " in steps of 32");
     SB_CHECK(act_ok(act), fn, ": unsupported activation dtype ", act);
-    const dim3 grid((unsigned)((d + 31) / 32), (unsigned)T);
     auto st = static_cast<cudaStream_t>(stream);
-    if (act == kF32) {
-        if (bits == 4) hc_up_kernel<float, 4><<<grid, 128, 0, st>>>(h, *w_up, (const float *)x, norm_w, inv, d, (float *)u);
-        else hc_up_kernel<float, 8><<<grid, 128, 0, st>>>(h, *w_up, (const float *)x, norm_w, inv, d, (float *)u);
-    } else {
-        if (bits == 4) hc_up_kernel<uint16_t, 4><<<grid, 128, 0, st>>>(h, *w_up, (const uint16_t *)x, norm_w, inv, d, (uint16_t *)u);
-        else hc_up_kernel<uint16_t, 8><<<grid, 128, 0, st>>>(h, *w_up, (const uint16_t *)x, norm_w, inv, d, (uint16_t *)u);
-    }
+    auto launch = [&](auto tag, auto bits_tag, auto mt_tag) {
+        using X = decltype(tag);
+        constexpr int B = decltype(bits_tag)::value, MT = decltype(mt_tag)::value;
+        const dim3 grid((unsigned)((d + 31) / 32), (unsigned)((T + MT - 1) / MT));
+        hc_up_kernel<X, B, MT><<<grid, 128, 0, st>>>(h, *w_up, (const X *)x, norm_w, inv, T, d, (X *)u);
+    };
+    auto by_batch = [&](auto tag, auto bits_tag) {
+        if (T < kBatchFrom) launch(tag, bits_tag, std::integral_constant<int, 1>{});
+        else launch(tag, bits_tag, std::integral_constant<int, kUpBatch>{});
+    };
+    auto by_bits = [&](auto tag) {
+        if (bits == 4) by_batch(tag, std::integral_constant<int, 4>{});
+        else by_batch(tag, std::integral_constant<int, 8>{});
+    };
+    if (act == kF32) by_bits(float{});
+    else by_bits(uint16_t{});
     SB_LAUNCH_OK(fn, " T=", T, " d=", d, " r=", w_up->K);
     return 0;
 }
