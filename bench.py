@@ -615,6 +615,9 @@ def reference_arm(args, name, cfg, line, emit):
     v = sample * k / dt
     line["config"] = config_of(name, cfg, 1, "n/a (host caches)")
     line["config"]["parallelism"] = "host cores (%d threads)" % base["cores"]
+    if cfg.get("ep"):  # the same declaration as the GPU arm's line for this workload
+        line["scaling"] = "strong"
+        line["config"]["router_bias"] = "Zipf(1.1)"
     line.update(impl="reference", value=v, steps=k, ms_per_step=1e3 * dt / k, n_gpus=args.gpus, gpu_launches=0,
                 dtype="f32" if cfg["act"] == "f32" else "bf16",
                 cpu_baseline=dict(value=v, unit="tokens/s", cores=base["cores"], kind="port",
