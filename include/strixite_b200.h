@@ -294,9 +294,10 @@ int strix_moe_layer_create(const strix_moe_layer_desc *desc, strix_moe_layer **o
 void strix_moe_layer_destroy(strix_moe_layer *layer);
 /* y[M, d] = MoE(x[M, d]) on device buffers. */
 int strix_moe_layer_forward(strix_moe_layer *layer, const void *x, int64_t M, void *y, void *stream);
-/* The same through HOST buffers: x is copied in through the layer's pinned staging area, y and the six error words
- * are copied back behind the kernels, one synchronization at the end (the reference's read_back,
- * runtime/qwen4exp.cpp:810-846). A raised error word fails the call like report_router_error / report_expert_error. */
+/* The same through HOST buffers: x is copied in, y and the six error words are copied back behind the kernels, one
+ * synchronization at the end (the reference's read_back, runtime/qwen4exp.cpp:810-846). Page-locked caller buffers
+ * (cudaHostAlloc / cudaHostRegister) are copied from and to directly; pageable ones pass through the layer's own page-locked
+ * staging area with a host memcpy each way. A raised error word fails the call like report_router_error / report_expert_error. */
 int strix_moe_layer_forward_host(strix_moe_layer *layer, const void *x_host, int64_t M, void *y_host, void *stream);
 /* x[M, d] += MoE_l(x) for l = 0 .. n_layers - 1 (residual_add between layers); tmp [M, d] is scratch. */
 int strix_moe_stack_forward(strix_moe_layer *const *layers, int64_t n_layers, void *x, int64_t M, void *tmp, void *stream);

@@ -402,13 +402,24 @@ int strix_moe_layer_forward_host(strix_moe_layer *L, const void *x_host, int64_t
     SB_CHECK(M >= 1 && M <= L->d.max_tokens, fn, ": ", M, " tokens, expected 1..", L->d.max_tokens);
     auto st = static_cast<cudaStream_t>(stream);
     const size_t bytes = (size_t)(M * L->d.d * act_size(L->d.act));
-    std::memcpy(L->pin_x, x_host, bytes);
-    SB_CUDA(cudaMemcpyAsync(L->dev_x, L->pin_x, bytes, cudaMemcpyHostToDevice, st), fn, ": x to the device");
+    // Page-locked caller buffers are copied from and to directly; pageable ones go through the layer's own page-locked staging
+    // (a host memcpy each way: ~10 GB/s on one core, which at thousands of tokens costs more than the layer itself).
+    auto page_locked = [](const void *p) {
+        cudaPointerAttributes a;
+        if (cudaPointerGetAttributes(&a, p) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return false;
+        }
+        return a.type == cudaMemoryTypeHost;
+    };
+    const bool x_direct = page_locked(x_host), y_direct = page_locked(y_host);
+    if (!x_direct) std::memcpy(L->pin_x, x_host, bytes);
+    SB_CUDA(cudaMemcpyAsync(L->dev_x, x_direct ? x_host : L->pin_x, bytes, cudaMemcpyHostToDevice, st), fn, ": x to the device");
     SB_TRY(strix_moe_layer_forward(L, L->dev_x, M, L->dev_y, stream));
-    SB_CUDA(cudaMemcpyAsync(L->pin_y, L->dev_y, bytes, cudaMemcpyDeviceToHost, st), fn, ": y to the host");
+    SB_CUDA(cudaMemcpyAsync(y_direct ? y_host : L->pin_y, L->dev_y, bytes, cudaMemcpyDeviceToHost, st), fn, ": y to the host");
     SB_CUDA(cudaMemcpyAsync(L->pin_err, L->err, 24, cudaMemcpyDeviceToHost, st), fn, ": error words to the host");
     SB_CUDA(cudaStreamSynchronize(st), fn, ": waiting for the layer");
-    std::memcpy(y_host, L->pin_y, bytes);
+    if (!y_direct) std::memcpy(y_host, L->pin_y, bytes);
     SB_TRY(strix_report_router_error(L->pin_err, "moe layer router"));
     SB_TRY(strix_report_expert_error(L->pin_err + 3, "moe layer experts"));
     return 0;

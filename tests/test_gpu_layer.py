@@ -174,6 +174,14 @@ def test_host_buffer_entry_matches_device_entry():
     y_dev = layer.forward(to_torch_act(x)).cpu().numpy()
     y_host = layer.forward_host(x)
     assert np.array_equal(y_dev, y_host)
+    # page-locked caller buffers are copied from and to directly (no staging memcpy): same result, also when only one side is
+    xp = torch.from_numpy(x).pin_memory()
+    yp = torch.empty_like(xp).pin_memory()
+    layer.forward_host(xp.numpy(), yp.numpy())
+    assert np.array_equal(y_dev, yp.numpy())
+    assert np.array_equal(y_dev, layer.forward_host(xp.numpy()))
+    layer.forward_host(x, yp.numpy())
+    assert np.array_equal(y_dev, yp.numpy())
 
 
 def test_host_entry_reports_nonfinite_input():
