@@ -1,7 +1,7 @@
 // Drop-in definitions of strixite's MoE-path kernel functions (namespace strix::kernels) over the C ABI of
 // libstrixite_b200.so: compile this file into the reference's strix_kernels target INSTEAD of the .hip files that define the
 // same functions (kernels/moe_router.hip, moe_grouped.hip, linear_q4.hip, linear_q56.hip, linear_q8.hip, linear.hip,
-// linear_wmma.hip, swiglu.hip, residual.hip and hc.hip), link libstrixite_b200.so, and runtime/qwen4exp.cpp builds
+// linear_wmma.hip, swiglu.hip, residual.hip, hc.hip and hc_wmma.hip), link libstrixite_b200.so, and runtime/qwen4exp.cpp builds
 // unchanged. The stream handle is passed through as an opaque pointer (a cudaStream_t on the B200 side).
 //
 // One function per declaration of the reference headers it includes; argument order and meaning are the reference's. A nonzero
@@ -162,7 +162,30 @@ void hc_mix_up(const float *h, const Q8ChunkMajorView &w_up, const void *x, cons
     const strix_qview v = qv(w_up);
     ok(strix_hc_mix_up(h, &v, 8, x, norm_w, inv, T, H, d, u, a(act), stream));
 }
-// kernels/hc_wmma.hpp:38-42 (the matrix-unit forms of the two mixes in that header stay with the reference's hc_wmma.hip)
+// kernels/hc_wmma.hpp:26-47. hc_inject_inv has its own entry. The many-token forms of the two mixes run the same entries as
+// hc_mix_down / hc_mix_up (from 16 tokens on those decode a weight chunk once per batch of tokens): the same math with FP32
+// instead of F16 operands, so the partials workspace is not used and inv is always recomputed from X (inv_ready only lets
+// the reference skip that pass; after hc_inject_inv it would hold the same values up to summation order).
+size_t hc_wmma_workspace_bytes(int64_t T, int64_t H, int64_t R) {
+    if (!(T >= 1 && H >= 1 && R >= 1)) throw Error("hc_wmma_workspace_bytes: T, H and R must be positive");
+    return (size_t)(H * T * R) * 4;  // the reference's size (kernels/hc_wmma.hip:368-371): callers allocate it either way
+}
+void hc_mix_down_wmma(const void *x, const Q4DeviceView &w, int64_t T, int64_t H, int64_t d, int64_t r, bool inject, float eps, float *h, float *w_in,
+                      float *inv, float *, size_t, Act act, hipStream_t stream, bool) {
+    hc_mix_down(x, w, T, H, d, r, inject, eps, h, w_in, inv, act, stream);
+}
+void hc_mix_down_wmma(const void *x, const Q8DeviceView &w, int64_t T, int64_t H, int64_t d, int64_t r, bool inject, float eps, float *h, float *w_in,
+                      float *inv, float *, size_t, Act act, hipStream_t stream, bool) {
+    hc_mix_down(x, w, T, H, d, r, inject, eps, h, w_in, inv, act, stream);
+}
+void hc_mix_up_wmma(const float *h, const Q4ChunkMajorView &w_up, const void *x, const float *norm_w, const float *inv, int64_t T, int64_t H, int64_t d,
+                    void *u, Act act, hipStream_t stream) {
+    hc_mix_up(h, w_up, x, norm_w, inv, T, H, d, u, act, stream);
+}
+void hc_mix_up_wmma(const float *h, const Q8ChunkMajorView &w_up, const void *x, const float *norm_w, const float *inv, int64_t T, int64_t H, int64_t d,
+                    void *u, Act act, hipStream_t stream) {
+    hc_mix_up(h, w_up, x, norm_w, inv, T, H, d, u, act, stream);
+}
 void hc_inject_inv(void *x, const float *w_in, const void *y, int64_t T, int64_t H, int64_t d, float eps, float *inv, Act act, hipStream_t stream) {
     ok(strix_hc_inject_inv(x, w_in, y, T, H, d, eps, inv, a(act), stream));
 }

@@ -25,7 +25,7 @@ def test_shim_matches_the_reference_declarations():
 def test_shim_defines_every_function_the_headers_declare():
     """Each function declared in the MoE-path headers (and the dense / tensor projections) has a definition in the shim."""
     headers = ["moe_router.hpp", "moe_grouped.hpp", "linear_q4.hpp", "linear_q5.hpp", "linear_q6.hpp", "linear_q8.hpp", "linear.hpp", "linear_wmma.hpp",
-               "swiglu.hpp", "residual.hpp"]
+               "swiglu.hpp", "residual.hpp", "hc.hpp", "hc_wmma.hpp"]
     declared = set()
     for h in headers:
         text = re.sub(r"//[^\n]*", "", open(os.path.join(REF, "kernels", h)).read())
