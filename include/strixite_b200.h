@@ -305,8 +305,9 @@ int strix_moe_stack_forward(strix_moe_layer *const *layers, int64_t n_layers, vo
  * device: ids[n] is each slot's expert in THIS layer's stacks (0 .. Estack - 1) and its activation row is
  * rows[row_index[i], :] (the layer's activation dtype), or rows[i, :] when row_index is NULL - with row_index a token
  * routed to several local experts is sent once. partial[i, :] = W_down[ids[i]] * SwiGLU(W_gate_up[ids[i]] * row), FP32
- * [n, d] or (partial_f16 != 0) F16 [n, d] - one rounding of each FP32 sum, half the bytes - without the routing coefficient. Groups the slots by expert and runs the tensor-core kernels; needs a layer created
- * with math != STRIX_MATH_F32 over uniform 4-bit stacks, and n <= max_tokens * (k + shared). Slots with an invalid id
+ * [n, d] or (partial_f16 != 0) F16 [n, d] - one rounding of each FP32 sum, half the bytes - without the routing coefficient.
+ * Groups the slots by expert and runs the tensor-core kernels; needs a layer created with math != STRIX_MATH_F32 over
+ * uniform 4-bit stacks, and n <= max_tokens * (k + shared). Slots with an invalid id
  * raise the expert error words and are left unwritten; an id of -2 marks an absent slot (padding of a fixed-capacity list):
  * skipped without an error. No counterpart in the reference (which has no expert parallelism). */
 int strix_moe_layer_experts_partial(strix_moe_layer *layer, const void *rows, const int32_t *row_index, const int32_t *ids,
